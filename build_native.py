@@ -41,11 +41,13 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-I",
 _SERVE_COMMON = ["common", "gemm", "activation", "moe", "comm/watchdog.cu"]    # the gated GEMM modes report expired flag waits through the watchdog
 COMPONENTS = {
     "serve": _SERVE_COMMON + ["norm", "rope", "swiglu", "serve", "attention/latent_attention.cu", "attention/latent_attention_t5.cu",
-                              "attention/pooled_window_attention.cu", "attention/pooled_window_attention_mma.cu"],
+                              "attention/pooled_window_attention.cu", "attention/pooled_window_attention_mma.cu",
+                              "attention/diff_attention.cu", "recurrent"],
     # what trace replay of one design needs and no more (the library grows when another component is asked for later)
     "serve-nafazen": _SERVE_COMMON + ["norm/scalar_rmsnorm.cu", "attention/latent_attention.cu", "attention/latent_attention_t5.cu"],
     "serve-teluzen": _SERVE_COMMON + ["norm/sandwich_norm.cu", "attention/pooled_window_attention.cu",
                                       "attention/pooled_window_attention_mma.cu"],
+    "serve-namisun": _SERVE_COMMON + ["norm/scalar_rmsnorm.cu", "norm/parallel_norm.cu", "attention/diff_attention.cu", "recurrent"],
     "all": None,
 }
 

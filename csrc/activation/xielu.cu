@@ -6,6 +6,8 @@
 //   gated SiLU   : out = silu(gate) * up on a packed [rows, 2F] activation (gate first) of either type
 //                  (csrc/swiglu/swiglu.cu is the bf16-only training kernel with a backward).
 //   squared ReLU : max(z, 0)^2
+//   clamped gate : g' = min(gate, limit), u' = clamp(up, -limit, limit); out = g' sigmoid(alpha g') (u' + 1), packed like
+//                  the gated SiLU
 // Reference: none (the reference has no model code).
 #include "../common/dtype.cuh"
 
@@ -32,6 +34,20 @@ gated_silu_kernel(const T* __restrict__ gu, long long ld, T* __restrict__ out, i
     const int c = static_cast<int>(i % F);
     const float g = to_f32(gu[r * ld + c]), u = to_f32(gu[r * ld + F + c]);
     out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_clamped_kernel(const T* __restrict__ gu, long long ld, T* __restrict__ out, int rows, int F, float limit, float alpha) {
+  const long long n = static_cast<long long>(rows) * F;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / F;
+    const int c = static_cast<int>(i % F);
+    const float g = fminf(to_f32(gu[r * ld + c]), limit);
+    const float u = fminf(fmaxf(to_f32(gu[r * ld + F + c]), -limit), limit);
+    out[i] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
   }
 }
 
@@ -67,6 +83,16 @@ LLMCTL_API int llmctl_gated_silu(const void* gate_up, long long ld, void* out, i
   if (rows == 0 || F == 0) return 0;
   LLMCTL_DISPATCH_DTYPE(is_fp32, T, (gated_silu_kernel<T><<<grid_for(static_cast<long long>(rows) * F), 256, 0, (cudaStream_t)stream>>>(
                                         (const T*)gate_up, ld, (T*)out, rows, F)));
+  LLMCTL_RETURN_LAST();
+}
+
+LLMCTL_API int llmctl_gated_clamped(const void* gate_up, long long ld, void* out, int is_fp32, int rows, int F, float limit, float alpha,
+                                    void* stream) {
+  LLMCTL_BEGIN();
+  LLMCTL_REQUIRE(ld >= 2LL * F && limit > 0.f);
+  if (rows == 0 || F == 0) return 0;
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (gated_clamped_kernel<T><<<grid_for(static_cast<long long>(rows) * F), 256, 0, (cudaStream_t)stream>>>(
+                                        (const T*)gate_up, ld, (T*)out, rows, F, limit, alpha)));
   LLMCTL_RETURN_LAST();
 }
 

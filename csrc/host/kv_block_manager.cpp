@@ -4,6 +4,10 @@
 // the paged-attention kernel K12 reads on the device).  Blocks are reference counted so forked sequences
 // share a prefix; the free list is LIFO so recently used blocks (still warm in L2) are reused first.
 //
+// Models with recurrent layers also keep a fixed-size state per sequence: the manager then owns a pool of state
+// slots beside the pages (llmctl_kv_set_state_slots).  A sequence takes a slot with its first page and gives it back
+// with its pages, so preemption, finishing and re-admission need no second bookkeeping.
+//
 // Reference: reference llmctl/serve/server.py:57-87 `KVCacheManager` is a request_id -> (k, v) dict with
 // LRU eviction whose set_cache() is never called.  Nothing of it is reused.
 #include "llmctl_host.h"
@@ -20,12 +24,15 @@ namespace {
 struct Seq {
   std::vector<int> blocks;
   int num_tokens = 0;
+  int state_slot = -1;
 };
 
 struct KV {
   int num_blocks, block_size, watermark_blocks;
   std::vector<int> free_list;
   std::vector<int> refcnt;
+  std::vector<int> free_slots;      // state slots not owned by a sequence (LIFO); empty and unused without recurrent layers
+  int num_slots = 0;
   std::unordered_map<long long, Seq> seqs;
   std::mutex mu;
 
@@ -50,9 +57,14 @@ API int llmctl_kv_allocate(void* h, long long seq_id, int num_tokens) {
   std::lock_guard<std::mutex> lk(kv->mu);
   Seq& s = kv->seqs[seq_id];
   const int need = kv->blocks_for(num_tokens) - static_cast<int>(s.blocks.size());
-  if (need > static_cast<int>(kv->free_list.size())) {
+  const bool wants_slot = kv->num_slots > 0 && s.state_slot < 0;
+  if (need > static_cast<int>(kv->free_list.size()) || (wants_slot && kv->free_slots.empty())) {
     if (s.blocks.empty() && s.num_tokens == 0) kv->seqs.erase(seq_id);
     return -1;
+  }
+  if (wants_slot) {
+    s.state_slot = kv->free_slots.back();
+    kv->free_slots.pop_back();
   }
   for (int i = 0; i < need; ++i) {
     const int b = kv->free_list.back();
@@ -76,8 +88,32 @@ API int llmctl_kv_free(void* h, long long seq_id) {
       ++released;
     }
   }
+  if (it->second.state_slot >= 0) kv->free_slots.push_back(it->second.state_slot);
   kv->seqs.erase(it);
   return released;
+}
+
+API int llmctl_kv_set_state_slots(void* h, int num_slots) {
+  KV* kv = static_cast<KV*>(h);
+  std::lock_guard<std::mutex> lk(kv->mu);
+  if (num_slots < 0 || !kv->seqs.empty()) return -1;
+  kv->num_slots = num_slots;
+  kv->free_slots.clear();
+  for (int i = num_slots - 1; i >= 0; --i) kv->free_slots.push_back(i);
+  return 0;
+}
+
+API int llmctl_kv_state_slot(void* h, long long seq_id) {
+  KV* kv = static_cast<KV*>(h);
+  std::lock_guard<std::mutex> lk(kv->mu);
+  auto it = kv->seqs.find(seq_id);
+  return it == kv->seqs.end() ? -1 : it->second.state_slot;
+}
+
+API int llmctl_kv_free_state_slots(void* h) {
+  KV* kv = static_cast<KV*>(h);
+  std::lock_guard<std::mutex> lk(kv->mu);
+  return static_cast<int>(kv->free_slots.size());
 }
 
 API int llmctl_kv_num_tokens(void* h, long long seq_id) {
@@ -116,6 +152,7 @@ API int llmctl_kv_fork(void* h, long long parent, long long child, int* cow_src,
   std::lock_guard<std::mutex> lk(kv->mu);
   auto it = kv->seqs.find(parent);
   if (it == kv->seqs.end() || kv->seqs.count(child)) return -1;
+  if (kv->num_slots > 0) return -1;  // a recurrent state cannot be shared: fork is for attention-only models
   Seq c = it->second;  // copy the table
   const bool partial = (c.num_tokens % kv->block_size) != 0 && !c.blocks.empty();
   if (partial && kv->free_list.empty()) return -1;

@@ -4,7 +4,12 @@
 //
 //   llmctl_moe_route   : per token, logits = Wr x (fp32), score = sigmoid or softmax over experts, the `top` largest
 //                        (ties: lowest index), optionally renormalised to sum 1; optional per-token gate
-//                        sigmoid(wg . x) of a shared expert; counts tokens per expert.
+//                        sigmoid(wg . x) of a shared expert; counts tokens per expert.  Optionally the CHOICE is made on
+//                        score + correction[e] (the weights stay the plain scores) and restricted to the
+//                        `keep_groups` of `n_groups` equal groups of neighbouring experts whose best choice score is
+//                        largest (the others count as minus infinity).  Expert ids >= the number of experts with
+//                        weights (`E` of plan / permute) are identity experts: they get no rows in the permuted
+//                        buffer and the combine adds weight * (the token's input) for them.
 //   llmctl_moe_plan    : one CTA: per-expert row offsets in the permuted buffer, every expert's segment padded to a
 //                        multiple of the GEMM's row tile, and the tile -> expert map.
 //   llmctl_moe_permute : copies every (token, choice) pair's input row into its expert's segment, multiplied by the
@@ -30,9 +35,10 @@ constexpr int kTileM = 64, kTileN = 64, kTileK = 16;
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const float* __restrict__ x, const T* __restrict__ wr, const T* __restrict__ wg, int W, int E, int top,
-                 int softmax_scores, int renormalise, int* __restrict__ ids, float* __restrict__ weights,
-                 float* __restrict__ gate, int* __restrict__ counts) {
-  extern __shared__ float score[];   // [E]
+                 int softmax_scores, int renormalise, const float* __restrict__ correction, int n_groups, int keep_groups,
+                 int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ gate, int* __restrict__ counts) {
+  extern __shared__ float score[];   // [E] scores, then [E] choice scores
+  float* choice = score + E;
   const long long tok = blockIdx.x;
   const float* xr = x + tok * W;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -68,19 +74,48 @@ moe_route_kernel(const float* __restrict__ x, const T* __restrict__ wr, const T*
     } else {
       for (int e = 0; e < E; ++e) score[e] = 1.f / (1.f + expf(-score[e]));
     }
+    for (int e = 0; e < E; ++e) choice[e] = score[e] + (correction ? correction[e] : 0.f);
+    if (n_groups > 1 && keep_groups < n_groups) {
+      // a group's score is its largest choice score; groups outside the best `keep_groups` cannot be chosen
+      const int gs = E / n_groups;
+      unsigned long long kept = 0ull;                  // n_groups <= 64
+      for (int r = 0; r < keep_groups; ++r) {
+        int bg = -1;
+        float bgv = -INFINITY;
+        for (int gi = 0; gi < n_groups; ++gi) {
+          if (kept >> gi & 1ull) continue;
+          float gv = -INFINITY;
+          for (int e = gi * gs; e < (gi + 1) * gs; ++e) gv = fmaxf(gv, choice[e]);
+          if (bg < 0 || gv > bgv) {
+            bgv = gv;
+            bg = gi;
+          }
+        }
+        kept |= 1ull << bg;
+      }
+      for (int e = 0; e < E; ++e)
+        if (!(kept >> (e / gs) & 1ull)) choice[e] = -INFINITY;
+    }
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
-      int best = 0;
+      int best = -1;
       float bv = -INFINITY;
       for (int e = 0; e < E; ++e)
-        if (score[e] > bv) {
-          bv = score[e];
+        if (choice[e] > bv || (best < 0 && choice[e] > -INFINITY)) {
+          bv = choice[e];
           best = e;
         }
+      if (best < 0) {                                  // fewer choosable experts than `top` (NaN scores): first unchosen one
+        for (int e = 0; e < E && best < 0; ++e) {
+          bool taken = false;
+          for (int kk = 0; kk < k; ++kk) taken |= ids[tok * top + kk] == e;
+          if (!taken) best = e;
+        }
+      }
       ids[tok * top + k] = best;
-      weights[tok * top + k] = bv;
-      total += bv;
-      score[best] = -INFINITY;
+      weights[tok * top + k] = score[best];
+      total += score[best];
+      choice[best] = -INFINITY;
       atomicAdd(&counts[best], 1);
     }
     if (softmax_scores == 2) {
@@ -89,7 +124,7 @@ moe_route_kernel(const float* __restrict__ x, const T* __restrict__ wr, const T*
       for (int k = 0; k < top; ++k) z += (weights[tok * top + k] = expf(weights[tok * top + k] - m));
       for (int k = 0; k < top; ++k) weights[tok * top + k] /= z;
     } else if (renormalise)
-      for (int k = 0; k < top; ++k) weights[tok * top + k] /= total;
+      for (int k = 0; k < top; ++k) weights[tok * top + k] /= total + 1e-20f;
   }
 }
 
@@ -120,10 +155,11 @@ moe_permute_kernel(const float* __restrict__ x, int W, const int* __restrict__ i
   const long long pair = blockIdx.x;
   if (threadIdx.x == 0) {
     const int e = ids[pair];
-    s_row = meta[e] + atomicAdd(&meta[E + e], 1);
+    s_row = e < E ? meta[e] + atomicAdd(&meta[E + e], 1) : -1;       // ids >= E: identity experts, no row
     pair_row[pair] = s_row;
   }
   __syncthreads();
+  if (s_row < 0) return;
   const long long tok = pair / top;
   const float w = scale_input ? weights[pair] : 1.f;
   const float* src = x + tok * W;
@@ -249,12 +285,17 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const T* __restrict__ expert_out, int W, const int* __restrict__ pair_row,
                    const float* __restrict__ weights, int top, int scale_output, const T* __restrict__ shared_out,
-                   const float* __restrict__ gate, float* __restrict__ y) {
+                   const float* __restrict__ gate, const float* __restrict__ identity_in, float* __restrict__ y) {
   const long long tok = blockIdx.x;
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
     float a = 0.f;
     for (int k = 0; k < top; ++k) {
-      const float v = to_f32(expert_out[static_cast<long long>(pair_row[tok * top + k]) * W + c]);
+      const int row = pair_row[tok * top + k];
+      if (row < 0) {                                   // an identity expert: weight times the token's input
+        a += weights[tok * top + k] * identity_in[tok * W + c];
+        continue;
+      }
+      const float v = to_f32(expert_out[static_cast<long long>(row) * W + c]);
       a += scale_output ? weights[tok * top + k] * v : v;
     }
     if (shared_out) a += (gate ? gate[tok] : 1.f) * to_f32(shared_out[tok * W + c]);
@@ -269,15 +310,18 @@ using namespace llmctl;
 LLMCTL_API int llmctl_moe_tile_rows() { return kTileM; }
 
 LLMCTL_API int llmctl_moe_route(const float* x, const void* wr, const void* wg, int is_fp32, int tokens, int W, int E, int top,
-                                int softmax_scores, int renormalise, int* ids, float* weights, float* gate, int* counts,
-                                void* stream) {
+                                int softmax_scores, int renormalise, const float* correction, int n_groups, int keep_groups,
+                                int* ids, float* weights, float* gate, int* counts, void* stream) {
   LLMCTL_BEGIN();
-  LLMCTL_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 8192 && (wg == nullptr || gate != nullptr));
+  LLMCTL_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 4096 && (wg == nullptr || gate != nullptr));
+  LLMCTL_REQUIRE(n_groups <= 1 || (n_groups <= 64 && E % n_groups == 0 && keep_groups >= 1 && keep_groups <= n_groups &&
+                                   keep_groups * (E / n_groups) >= top));
   cudaStream_t s = (cudaStream_t)stream;
   LLMCTL_CHECK(cudaMemsetAsync(counts, 0, sizeof(int) * E, s));
   if (tokens == 0) return 0;
-  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (moe_route_kernel<T><<<tokens, 256, E * sizeof(float), s>>>(
-                                        x, (const T*)wr, (const T*)wg, W, E, top, softmax_scores, renormalise, ids, weights, gate, counts)));
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (moe_route_kernel<T><<<tokens, 256, 2 * E * sizeof(float), s>>>(
+                                        x, (const T*)wr, (const T*)wg, W, E, top, softmax_scores, renormalise, correction, n_groups,
+                                        keep_groups, ids, weights, gate, counts)));
   LLMCTL_RETURN_LAST();
 }
 
@@ -317,11 +361,11 @@ LLMCTL_API int llmctl_grouped_gemm(const void* A, long long lda, const void* Wt,
 }
 
 LLMCTL_API int llmctl_moe_combine(const void* expert_out, int W, const int* pair_row, const float* weights, int top,
-                                  int scale_output, const void* shared_out, const float* gate, float* y, int tokens,
-                                  int is_fp32, void* stream) {
+                                  int scale_output, const void* shared_out, const float* gate, const float* identity_in,
+                                  float* y, int tokens, int is_fp32, void* stream) {
   LLMCTL_BEGIN();
   if (tokens == 0) return 0;
   LLMCTL_DISPATCH_DTYPE(is_fp32, T, (moe_combine_kernel<T><<<tokens, 256, 0, (cudaStream_t)stream>>>(
-                                        (const T*)expert_out, W, pair_row, weights, top, scale_output, (const T*)shared_out, gate, y)));
+                                        (const T*)expert_out, W, pair_row, weights, top, scale_output, (const T*)shared_out, gate, identity_in, y)));
   LLMCTL_RETURN_LAST();
 }

@@ -170,7 +170,10 @@ def resolve_model(spec: str | Path | Dict[str, Any] | ModelConfig):
             arch = registry.architecture_named(raw["architecture"])
             if arch is None:
                 raise ValueError(f"unknown architecture {raw['architecture']!r}; known: {registry.architecture_names()}")
-            return arch.config_from_dict(raw)
+            cfg = arch.config_from_dict(raw)
+            if arch.complete_config is not None:
+                arch.complete_config(cfg, p)
+            return cfg
         return from_hf_config(raw, name=p.name)
     if p.exists() and p.is_dir():
         raise FileNotFoundError(f"{p} has neither model_config.json nor an HF config.json")

@@ -4,7 +4,7 @@ routed mixture of gated experts (sigmoid, softmax or chosen-logit softmax weight
 Reference: none — the reference has no model code (reference llmctl/runtime/engine.py:119-140)."""
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn
@@ -59,14 +59,25 @@ class GatedExpertMoE(nn.Module):
     all experts, ``softmax_scores`` True; or, ``softmax_scores`` 2, the largest logits are chosen and weighted by a
     softmax over the chosen logits only), optionally renormalised over the chosen ones; the score multiplies the expert's input
     (``scale_input``) or its output.  A shared expert of its own size runs for every token, times sigmoid(wg . h)
-    when ``shared_gate``."""
+    when ``shared_gate``.  Optional parts: ``identity`` further router outputs behind the experts stand for identity
+    experts (output = input, no weights); ``correction``: a learned vector added to the scores for the choice only;
+    ``groups`` = (count, keep): the router outputs form ``count`` equal groups of neighbours and only the ``keep`` groups
+    with the largest best choice score can be chosen from; ``clamp`` = (limit, alpha): the experts compute
+    ``g sigmoid(alpha g) (u + 1)`` on ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)`` instead of the gated
+    SiLU."""
 
     def __init__(self, width: int, experts: int, top: int, ff: int, shared_ff: Optional[int], dtype, device, *,
-                 scale_input: bool = True, softmax_scores: bool = False, renormalise: bool = False, shared_gate: bool = True):
+                 scale_input: bool = True, softmax_scores: bool = False, renormalise: bool = False, shared_gate: bool = True,
+                 identity: int = 0, correction: bool = False, groups: Optional[Tuple[int, int]] = None,
+                 clamp: Optional[Tuple[float, float]] = None):
         super().__init__()
         kw = dict(dtype=dtype, device=device)
         self.top, self.scale_input, self.softmax_scores, self.renormalise = top, scale_input, softmax_scores, renormalise
-        self.router = nn.Parameter(torch.empty(experts, width, **kw))
+        self.groups, self.clamp = groups, clamp
+        if groups and ((experts + identity) % groups[0] or not 1 <= groups[1] <= groups[0] or groups[1] * ((experts + identity) // groups[0]) < top):
+            raise ValueError(f"expert groups {groups} do not fit {experts} + {identity} router outputs with {top} choices")
+        self.router = nn.Parameter(torch.empty(experts + identity, width, **kw))
+        self.correction = nn.Parameter(torch.zeros(experts + identity, dtype=torch.float32, device=device)) if correction else None
         self.gate_up = nn.Parameter(torch.empty(experts, 2 * ff, width, **kw))
         self.down = nn.Parameter(torch.empty(experts, width, ff, **kw))
         self.shared_gate_up = nn.Parameter(torch.empty(2 * shared_ff, width, **kw)) if shared_ff else None
@@ -74,9 +85,11 @@ class GatedExpertMoE(nn.Module):
         self.shared_gate = nn.Parameter(torch.empty(width, **kw)) if shared_ff and shared_gate else None
 
     def load(self, get, prefix: str) -> None:
-        E = self.router.shape[0]
+        E = self.gate_up.shape[0]
         with torch.no_grad():
             self.router.copy_(get(prefix + "router"))
+            if self.correction is not None:
+                self.correction.copy_(get(prefix + "correction").float())
             for e in range(E):
                 self.gate_up[e].copy_(torch.cat([get(f"{prefix}e{e}.gate"), get(f"{prefix}e{e}.up")], dim=0))
                 self.down[e].copy_(get(f"{prefix}e{e}.down"))
@@ -94,4 +107,4 @@ class GatedExpertMoE(nn.Module):
             shared = ops.linear(eops.gated_silu(ops.linear(h, self.shared_gate_up)), self.shared_down)
         return mops.moe_ffn(x32, h.dtype, self.router, self.gate_up, self.down, self.top, scale_input=self.scale_input,
                             shared_out=shared, w_shared_gate=self.shared_gate, softmax=self.softmax_scores,
-                            renormalise=self.renormalise)
+                            renormalise=self.renormalise, correction=self.correction, groups=self.groups, clamp=self.clamp)

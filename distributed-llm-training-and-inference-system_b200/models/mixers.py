@@ -25,17 +25,42 @@ the layer's values with the values the first such layer computed for the same to
     o        = attention over window + pooled rows           (ops.window_attention.pooled_window_attention)
     out      = o Wo^T
 
+``DifferentialAttention``: grouped-query attention in which every head has two score maps (two query vectors against
+two key vectors of its key/value head) over the same values; the head's output is ``a1 - lam a2`` brought to unit RMS,
+times ``1 - diff`` and, optionally, a sigmoid gate per (token, head).  ``lam = exp(lq1 . lk1) - exp(lq2 . lk2) + diff`` is
+one number of the layer.  Partial interleaved rotation on every query and key vector.  Per step:
+
+    p        = h Wp^T                           (one packed GEMM: q | k | v | gate logits)
+    q, cache = rotate / append                  (ops.diff_attention.rotary_kv_append)
+    o        = both maps, difference, norm, gate        (ops.diff_attention.diff_attention)
+    out      = o Wo^T
+
+``GatedLinearAttention`` and ``SelectiveScan`` are recurrences: they keep no per-token cache but ONE state per sequence
+in a state slot (``serve/ragged.py`` ``RaggedBatch.portions`` names each portion's slot), fp32.
+
+``GatedLinearAttention``: per head ``S <- diag(a) S + k v^T``, ``o = S^T q`` with a decay per key channel
+``a = sigmoid(z)^(1/tau)``, ``z`` from a low-rank projection with bias; heads are RMS-normed with one shared weight,
+gated by ``silu`` of a projection and projected out.  Per step: one packed GEMM (q | k | v | gate | decay latent), the small
+decay GEMM, ``ops.recurrent.gla_scan``, ``ops.recurrent.gla_output``, the output GEMM.
+
+``SelectiveScan`` (Mamba): ``[x | z] = h Win^T``; ``u = silu(causal conv(x))``; ``[dt | B | C] = u Wx^T``;
+``dt = softplus(dt Wdt^T + b)``; ``S <- exp(dt A) S + dt u B``, ``y = (S C + D u) silu(z)``; output GEMM.  The state of a
+sequence is S and the last ``taps - 1`` inputs of the convolution.
+
 Reference: none — the reference has no model code (reference llmctl/runtime/engine.py:119-140)."""
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
-from typing import Any, Dict, Optional
+from typing import Any, Dict, Optional, Tuple
 
 import torch
 import torch.nn as nn
 
+from ..ops import diff_attention as dops
 from ..ops import functional as ops
 from ..ops import latent_attention as lops
+from ..ops import recurrent as rops
 from ..ops import window_attention as wops
 from ..ops.elementwise import rope_frequencies
 
@@ -215,3 +240,189 @@ class PooledWindowAttention(nn.Module):
                                          s.scale, s.heads, s.kv_heads, s.dim, s.vdim, s.window, pool, bs, h.dtype,
                                          max_context=batch.max_context)
         return ops.linear(o, self.w_o), v_first
+
+
+@dataclass
+class DifferentialAttentionSpec:
+    heads: int
+    kv_heads: int
+    dim: int            # size of each of the two query / key vectors of a head
+    vdim: int           # value size per head
+    scale: float
+    diff: float         # the constant in lam; the output is multiplied by 1 - diff
+    rot_dims: int = 0   # rotated numbers per query / key vector (even, <= dim); 0: no rotation
+    rot_base: float = 10000.0
+    rot_scaling: Optional[Dict[str, Any]] = None
+    head_gate: bool = True      # sigmoid gate per (token, head) from a projection of the mixer's input
+
+    @property
+    def cache_width(self) -> int:
+        return self.kv_heads * (2 * self.dim + self.vdim)
+
+
+class DifferentialAttention(nn.Module):
+    TILE_TOKENS = dops.TILE_TOKENS      # tile width of the ragged batch this mixer asks for (serve/ragged.py)
+    stateful = False
+
+    def __init__(self, width: int, spec: DifferentialAttentionSpec, eps: float, dtype, device):
+        super().__init__()
+        s = self.spec = spec
+        if s.heads % s.kv_heads or s.rot_dims % 2 or s.rot_dims > s.dim:
+            raise ValueError(f"inconsistent attention sizes: {s}")
+        self.eps = eps
+        kw = dict(dtype=dtype, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        self.nq, self.nk, self.nv = s.heads * 2 * s.dim, s.kv_heads * 2 * s.dim, s.kv_heads * s.vdim
+        self.w_in = nn.Parameter(torch.empty(self.nq + self.nk + self.nv + (s.heads if s.head_gate else 0), width, **kw))   # [q ; k ; v ; g]
+        self.lam_q = nn.Parameter(torch.zeros(2, s.dim, **f32))
+        self.lam_k = nn.Parameter(torch.zeros(2, s.dim, **f32))
+        self.w_o = nn.Parameter(torch.empty(width, s.heads * s.vdim, **kw))
+        if s.rot_dims:
+            f, self.rot_mult = rope_frequencies(s.rot_dims, s.rot_base, s.rot_scaling)
+        else:
+            f, self.rot_mult = torch.zeros(1), 1.0
+        self.register_buffer("rot_freq", f.to(device), persistent=False)
+        self._lam: Optional[float] = None
+
+    def load(self, get, prefix: str) -> None:
+        """Checkpoint names under ``prefix``: q, k, v, g ([heads, width]), lq1, lk1, lq2, lk2, o."""
+        s = self.spec
+        with torch.no_grad():
+            parts = [get(prefix + "q"), get(prefix + "k"), get(prefix + "v")] + ([get(prefix + "g")] if s.head_gate else [])
+            self.w_in.copy_(torch.cat(parts, dim=0))
+            self.lam_q.copy_(torch.stack([get(prefix + "lq1").float(), get(prefix + "lq2").float()]))
+            self.lam_k.copy_(torch.stack([get(prefix + "lk1").float(), get(prefix + "lk2").float()]))
+            self.w_o.copy_(get(prefix + "o"))
+        self._lam = None
+
+    @property
+    def lam(self) -> float:
+        """``exp(lq1 . lk1) - exp(lq2 . lk2) + diff``, evaluated once in fp32."""
+        if self._lam is None:
+            dots = (self.lam_q.detach().float() * self.lam_k.detach().float()).sum(-1).cpu()
+            e = torch.exp(dots)
+            self._lam = float(e[0] - e[1] + torch.tensor(self.spec.diff, dtype=torch.float32))
+        return self._lam
+
+    def cache_shape(self, num_blocks: int, block_size: int) -> Tuple[int, ...]:
+        return (num_blocks, block_size, self.spec.cache_width)
+
+    def forward(self, h: torch.Tensor, batch, cache: torch.Tensor) -> torch.Tensor:
+        """h: [T, W] in the activation type; ``cache``: this layer run's [pages, bs, G (2 d + e)]."""
+        s = self.spec
+        p = ops.linear(h, self.w_in)
+        q = dops.rotary_kv_append(p, 2 * s.heads, 2 * s.kv_heads, s.dim, self.nv, s.rot_dims, self.rot_freq, self.rot_mult,
+                                  batch.positions, batch.slots, cache)
+        gate = p[:, self.nq + self.nk + self.nv:] if s.head_gate else None
+        o = dops.diff_attention(q, cache, batch.block_tables, batch.tiles(self.TILE_TOKENS), 1 if batch.decode_only else self.TILE_TOKENS,
+                                batch.positions, gate, s.scale, self.lam, 1.0 - s.diff, self.eps, s.heads, s.kv_heads, s.dim, s.vdim,
+                                batch.block_size, h.dtype, max_context=batch.max_context)
+        return ops.linear(o, self.w_o)
+
+
+@dataclass
+class GatedLinearAttentionSpec:
+    heads: int
+    dim: int            # query / key size per head
+    vdim: int           # value size per head
+    tau: float          # the decay is sigmoid(z)^(1/tau)
+    decay_rank: int     # inner size of the low-rank decay projection
+
+
+class GatedLinearAttention(nn.Module):
+    stateful = True
+
+    def __init__(self, width: int, spec: GatedLinearAttentionSpec, eps: float, dtype, device):
+        super().__init__()
+        s = self.spec = spec
+        self.eps = eps
+        kw = dict(dtype=dtype, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        self.nk, self.nv = s.heads * s.dim, s.heads * s.vdim
+        self.w_in = nn.Parameter(torch.empty(2 * self.nk + 2 * self.nv + s.decay_rank, width, **kw))     # [q ; k ; v ; g ; a1]
+        self.w_a2 = nn.Parameter(torch.empty(self.nk, s.decay_rank, **kw))
+        self.b_a2 = nn.Parameter(torch.zeros(self.nk, **f32))
+        self.norm = nn.Parameter(torch.ones(s.vdim, **f32))
+        self.w_o = nn.Parameter(torch.empty(width, self.nv, **kw))
+
+    def load(self, get, prefix: str) -> None:
+        """Checkpoint names under ``prefix``: q, k, v, g, a1, a2 (+ ``a2.b``), norm, o."""
+        with torch.no_grad():
+            self.w_in.copy_(torch.cat([get(prefix + n) for n in ("q", "k", "v", "g", "a1")], dim=0))
+            self.w_a2.copy_(get(prefix + "a2"))
+            self.b_a2.copy_(get(prefix + "a2.b").float())
+            self.norm.copy_(get(prefix + "norm").float())
+            self.w_o.copy_(get(prefix + "o"))
+
+    def state_shapes(self) -> Tuple[Tuple[int, ...], ...]:
+        s = self.spec
+        return ((s.heads, s.dim, s.vdim),)
+
+    def forward(self, h: torch.Tensor, batch, state) -> torch.Tensor:
+        """h: [T, W] in the activation type; ``state``: (this layer run's [slots, H, d, e] fp32,)."""
+        s = self.spec
+        nk, nv = self.nk, self.nv
+        p = ops.linear(h, self.w_in)
+        z = ops.linear(p[:, 2 * nk + 2 * nv:], self.w_a2)
+        o = rops.gla_scan(p[:, :nk], p[:, nk:2 * nk], p[:, 2 * nk:2 * nk + nv], z, self.b_a2, batch.portions, state[0], s.heads, s.dim,
+                          s.vdim, s.dim ** -0.5, s.tau)
+        y = rops.gla_output(o, self.norm, p[:, 2 * nk + nv:2 * nk + 2 * nv], s.heads, s.vdim, self.eps, h.dtype)
+        return ops.linear(y, self.w_o)
+
+
+@dataclass
+class SelectiveScanSpec:
+    inner: int          # channels
+    state: int          # state numbers per channel (N)
+    dt_rank: int
+    conv: int           # taps of the causal convolution
+
+
+class SelectiveScan(nn.Module):
+    stateful = True
+
+    def __init__(self, width: int, spec: SelectiveScanSpec, dtype, device):
+        super().__init__()
+        s = self.spec = spec
+        if s.conv < 1:
+            raise ValueError("the convolution needs at least one tap")
+        kw = dict(dtype=dtype, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        self.w_in = nn.Parameter(torch.empty(2 * s.inner, width, **kw))                 # [x ; z]
+        self.conv_w = nn.Parameter(torch.empty(s.inner, s.conv, **f32))
+        self.conv_b = nn.Parameter(torch.zeros(s.inner, **f32))
+        self.w_x = nn.Parameter(torch.empty(s.dt_rank + 2 * s.state, s.inner, **kw))    # [dt ; B ; C]
+        self.w_dt = nn.Parameter(torch.empty(s.inner, s.dt_rank, **kw))
+        self.dt_bias = nn.Parameter(torch.zeros(s.inner, **f32))
+        self.A = nn.Parameter(-torch.ones(s.inner, s.state, **f32))                    # -exp(A_log), fp32
+        self.D = nn.Parameter(torch.ones(s.inner, **f32))
+        self.w_o = nn.Parameter(torch.empty(width, s.inner, **kw))
+
+    def load(self, get, prefix: str) -> None:
+        """Checkpoint names under ``prefix``: in, conv (+ ``conv.b``), x, dt (+ ``dt.b``), A_log, D, o."""
+        with torch.no_grad():
+            self.w_in.copy_(get(prefix + "in"))
+            self.conv_w.copy_(get(prefix + "conv").float())
+            self.conv_b.copy_(get(prefix + "conv.b").float())
+            self.w_x.copy_(get(prefix + "x"))
+            self.w_dt.copy_(get(prefix + "dt"))
+            self.dt_bias.copy_(get(prefix + "dt.b").float())
+            self.A.copy_(-torch.exp(get(prefix + "A_log").float()))
+            self.D.copy_(get(prefix + "D").float())
+            self.w_o.copy_(get(prefix + "o"))
+
+    def state_shapes(self) -> Tuple[Tuple[int, ...], ...]:
+        s = self.spec
+        return ((s.inner, s.state), (max(s.conv - 1, 0), s.inner))
+
+    def forward(self, h: torch.Tensor, batch, state) -> torch.Tensor:
+        """h: [T, W] in the activation type; ``state``: this layer run's ([slots, C, N], [slots, taps - 1, C]) fp32."""
+        s = self.spec
+        C, R, N = s.inner, s.dt_rank, s.state
+        xz = ops.linear(h, self.w_in)
+        x, z = xz[:, :C], xz[:, C:]
+        u = rops.causal_conv_silu(x, self.conv_w, self.conv_b, batch.portions, batch.seq_rows, state[1])
+        bc = ops.linear(u, self.w_x)
+        dtp = ops.linear(bc[:, :R], self.w_dt)
+        y = rops.selective_scan(u, bc, R, R + N, dtp, self.dt_bias, self.A, self.D, z, x, batch.portions, state[0], state[1])
+        return ops.linear(y, self.w_o)

@@ -17,6 +17,8 @@ class Architecture:
     config_type: type
     build: Callable[..., Any]                               # (cfg, dtype=, device=, **kw) -> nn.Module
     load_weights: Optional[Callable[[Any, Any], None]] = None   # (model, checkpoint directory) -> None
+    # (configuration, checkpoint directory) -> None: fills in sizes that only the checkpoint's tensor shapes give
+    complete_config: Optional[Callable[[Any, Any], None]] = None
 
 
 _BY_NAME: Dict[str, Architecture] = {}

@@ -2,8 +2,11 @@
 update with a single gain, scalar-gain RMS norm of selected rows, scaled embedding lookup, logit soft-capping, xIELU
 and gated SiLU, plus the frequency spectrum of interleaved-pair rotary embeddings (plain or YaRN-blended); for the
 sandwich layout (a weighted RMS norm before and after every sublayer): embedding plus learned position vector,
-weighted RMS norm of rows, fused out-norm + residual + next in-norm, and the squared ReLU.
-CUDA tensors run the kernels in csrc/norm/scalar_rmsnorm.cu, csrc/norm/sandwich_norm.cu and csrc/activation/xielu.cu;
+weighted RMS norm of rows, fused out-norm + residual + next in-norm, and the squared ReLU; for the parallel layout (one
+layer norm feeds mixer and feed-forward): layer norm of rows and the fused residual update + next layer norm, and the
+clamped gate activation.
+CUDA tensors run the kernels in csrc/norm/scalar_rmsnorm.cu, csrc/norm/sandwich_norm.cu, csrc/norm/parallel_norm.cu and
+csrc/activation/xielu.cu;
 CPU tensors run the PyTorch restatement below (CPU tests).  Sums, gains and the residual stream are fp32 in both.
 
 Reference: none — the reference has no model code (reference llmctl/runtime/engine.py:119-140 loads HF models)."""
@@ -27,6 +30,11 @@ native.register_signature("llmctl_gated_silu", [c_void_p, c_ll, c_void_p, c_int,
 native.register_signature("llmctl_relu_squared", [c_void_p, c_void_p, c_int, c_ll, c_void_p])
 native.register_signature("llmctl_embed_positions", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
 native.register_signature("llmctl_rmsnorm_rows", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+native.register_signature("llmctl_gated_clamped", [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p])
+native.register_signature("llmctl_layernorm_rows", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                                     c_float, c_void_p])
+native.register_signature("llmctl_parallel_residual", [c_void_p, c_int, c_ll, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                                        c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
 native.register_signature("llmctl_sandwich_residual", [c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                                         c_int, c_float, c_void_p])
 
@@ -41,11 +49,14 @@ def rope_frequencies(dims: int, base: float, scaling: Optional[Dict[str, Any]] =
     """Per-pair frequencies ``f_i = base^(-2i/dims)`` (fp32, [dims/2]) and the factor applied to cos and sin.
     ``scaling`` = {factor, original, fast, slow} blends towards ``f_i / factor`` between the pairs that make
     ``fast`` and ``slow`` turns over ``original`` positions (YaRN), and raises the cos/sin amplitude to
-    ``0.1 ln(factor) + 1``."""
+    ``0.1 ln(factor) + 1``.  ``scaling`` = {factor} alone divides every frequency by ``factor`` (linear position
+    interpolation)."""
     i = torch.arange(dims // 2, dtype=torch.float64)
     f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
     mult = 1.0
-    if scaling:
+    if scaling and "original" not in scaling:
+        f = f / float(scaling["factor"])
+    elif scaling:
         factor, orig = float(scaling["factor"]), float(scaling["original"])
 
         def pair_of(turns: float) -> float:
@@ -202,5 +213,74 @@ def sandwich_residual(y: torch.Tensor, x: torch.Tensor, w_out: torch.Tensor, w_n
     if w_next is None:
         return (None, None) if want_fp32 else None
     h32 = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w_next
+    h = h32.to(act_dtype)
+    return (h, h32) if want_fp32 else h
+
+
+def gated_clamped(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """``g sigmoid(alpha g) (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)`` of a packed
+    [rows, 2F] activation (gate first), bf16 or fp32."""
+    rows, F2 = gate_up.shape
+    if gate_up.is_cuda:
+        assert gate_up.stride(1) == 1
+        out = torch.empty(rows, F2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+        native.call("llmctl_gated_clamped", gate_up.data_ptr(), gate_up.stride(0), out.data_ptr(), _is32(gate_up), rows, F2 // 2,
+                    float(limit), float(alpha), native.stream_ptr())
+        return out
+    g, u = gate_up.float().chunk(2, dim=-1)
+    g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+    return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(gate_up.dtype)
+
+
+def _layernorm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float) -> torch.Tensor:
+    mu = x.mean(-1, keepdim=True)
+    return (x - mu) / torch.sqrt((x - mu).pow(2).mean(-1, keepdim=True) + eps) * w + b
+
+
+def layernorm_rows(x: torch.Tensor, rows: Optional[torch.Tensor], w: torch.Tensor, b: torch.Tensor, eps: float,
+                   out_dtype: torch.dtype, add: Optional[torch.Tensor] = None, want_fp32: bool = False):
+    """Layer norm ``(x - mean) / sqrt(var + eps) * w + b`` of the fp32 stream's rows (all when ``rows`` is None) in
+    ``out_dtype``; ``add`` (fp32 [W], only with all rows) is first added to the stream in place.  ``want_fp32``: returns
+    (normed in ``out_dtype``, the same before rounding)."""
+    n = x.shape[0] if rows is None else rows.numel()
+    assert x.dtype == torch.float32 and x.is_contiguous() and w.dtype == torch.float32 and b.dtype == torch.float32
+    assert add is None or rows is None
+    if x.is_cuda:
+        out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device)
+        out32 = torch.empty(n, x.shape[1], dtype=torch.float32, device=x.device) if want_fp32 and out_dtype != torch.float32 else None
+        native.call("llmctl_layernorm_rows", x.data_ptr(), native.ptr(rows), native.ptr(add), w.data_ptr(), b.data_ptr(), out.data_ptr(),
+                    int(out_dtype == torch.float32), native.ptr(out32), n, x.shape[1], float(eps), native.stream_ptr())
+        return (out, out if out32 is None else out32) if want_fp32 else out
+    if add is not None:
+        x += add
+    h32 = _layernorm(x if rows is None else x[rows], w, b, eps)
+    h = h32.to(out_dtype)
+    return (h, h32) if want_fp32 else h
+
+
+def parallel_residual(a: torch.Tensor, f: Optional[torch.Tensor], x: torch.Tensor, mult: float, eps: float, act_dtype: torch.dtype,
+                      w_next: Optional[torch.Tensor] = None, b_next: Optional[torch.Tensor] = None,
+                      add: Optional[torch.Tensor] = None, want_fp32: bool = False):
+    """``x += mult * (a + f)`` in place on the fp32 stream (a: [T, W] mixer output, bf16 or fp32; f: fp32 feed-forward
+    output or None), then ``x += add`` if given; with ``w_next`` / ``b_next`` also returns the layer norm of the new
+    stream (the next layer's input) from the same pass, as ``layernorm_rows`` does."""
+    T, W = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and a.shape == x.shape and a.stride(1) == 1
+    assert f is None or (f.dtype == torch.float32 and f.is_contiguous() and f.shape == x.shape)
+    if x.is_cuda:
+        out = torch.empty(T, W, dtype=act_dtype, device=x.device) if w_next is not None else None
+        out32 = None
+        if want_fp32 and w_next is not None and act_dtype != torch.float32:
+            out32 = torch.empty(T, W, dtype=torch.float32, device=x.device)
+        native.call("llmctl_parallel_residual", a.data_ptr(), _is32(a), a.stride(0), native.ptr(f), x.data_ptr(), float(mult),
+                    native.ptr(add), native.ptr(w_next), native.ptr(b_next), native.ptr(out), int(act_dtype == torch.float32),
+                    native.ptr(out32), T, W, float(eps), native.stream_ptr())
+        return (out, out if out32 is None else out32) if want_fp32 else out
+    x += mult * (a.float() + (f if f is not None else 0.0))
+    if add is not None:
+        x += add
+    if w_next is None:
+        return (None, None) if want_fp32 else None
+    h32 = _layernorm(x, w_next, b_next, eps)
     h = h32.to(act_dtype)
     return (h, h32) if want_fp32 else h

@@ -244,7 +244,11 @@ class InferenceEngine:
                 num_kv_blocks = 512
             want = (max_batch_tokens + kv_block_size - 1) // kv_block_size + max_batch_size
             num_kv_blocks = max(min(num_kv_blocks, 8 * want), want)
-        self.kv = KVBlockManager(num_kv_blocks, kv_block_size, kv_watermark)
+        # models with recurrent layers keep one state per sequence: the block manager hands out a state slot with a
+        # sequence's first page and takes it back with its pages (finish, preemption), one slot per batch seat
+        self.stateful = self.ragged and bool(getattr(m, "stateful", False))
+        self.state_slots = max_batch_size if self.stateful else 0
+        self.kv = KVBlockManager(num_kv_blocks, kv_block_size, kv_watermark, state_slots=self.state_slots)
         # a scheduler plugin (user-guide contract: ``schedule(requests) -> ordered requests``) decides the ORDER in
         # which waiting requests are handed to the native continuous-batching core; budgets, KV accounting and
         # preemption stay in the C++ scheduler
@@ -259,7 +263,10 @@ class InferenceEngine:
             self._plugin_sched = factory() if callable(factory) else factory
             scheduler = "dynamic"
         self.sched = BatchScheduler(max_batch_size, max_batch_tokens, scheduler, self.kv)
-        if self.ragged:
+        if self.stateful:
+            self.caches = m.allocate_caches(num_kv_blocks, kv_block_size, self.device, state_slots=self.state_slots)
+            self.k_caches, self.v_caches = [], []
+        elif self.ragged:
             self.caches = m.allocate_caches(num_kv_blocks, kv_block_size, self.device)
             self.k_caches, self.v_caches = [], []
         else:
@@ -382,7 +389,7 @@ class InferenceEngine:
         return g[2][:B]
 
     def portion(self, seq_id: int, tokens: List[int], start: int, want: List[int]) -> Portion:
-        return Portion(seq_id, tokens, start, want, self.kv.block_table(seq_id))
+        return Portion(seq_id, tokens, start, want, self.kv.block_table(seq_id), self.kv.state_slot(seq_id) if self.stateful else -1)
 
     def _step_ragged(self, plan) -> List[Sequence]:
         """Prefills (whole prompt, or prompt + generated tokens after a preemption) and decodes of one scheduler step

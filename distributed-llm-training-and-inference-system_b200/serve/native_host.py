@@ -30,6 +30,8 @@ def lib() -> ctypes.CDLL:
             "llmctl_kv_free_blocks": (c_int, [c_void_p]), "llmctl_kv_total_blocks": (c_int, [c_void_p]),
             "llmctl_kv_block_size": (c_int, [c_void_p]), "llmctl_kv_can_allocate": (c_int, [c_void_p, c_int]),
             "llmctl_kv_fork": (c_int, [c_void_p, c_ll, c_ll, PI, PI]),
+            "llmctl_kv_set_state_slots": (c_int, [c_void_p, c_int]), "llmctl_kv_state_slot": (c_int, [c_void_p, c_ll]),
+            "llmctl_kv_free_state_slots": (c_int, [c_void_p]),
             "llmctl_sched_create": (c_void_p, [c_int, c_int, c_int, c_void_p]),
             "llmctl_sched_destroy": (None, [c_void_p]), "llmctl_sched_add": (c_int, [c_void_p, c_ll, c_int, c_int]),
             "llmctl_sched_step": (c_int, [c_void_p, PLL, PI, PI, c_int]),
@@ -47,11 +49,15 @@ def lib() -> ctypes.CDLL:
 class KVBlockManager:
     """Paged KV bookkeeping (reference llmctl/serve/server.py:57-87 ``KVCacheManager`` is an unused LRU dict)."""
 
-    def __init__(self, num_blocks: int, block_size: int = 16, watermark: float = 0.01):
+    def __init__(self, num_blocks: int, block_size: int = 16, watermark: float = 0.01, state_slots: int = 0):
+        """``state_slots``: per-sequence state slots for models with recurrent layers (0 = none).  A sequence takes one
+        with its first page and returns it in ``free``; ``allocate`` fails when none is left."""
         self._h = lib().llmctl_kv_create(num_blocks, block_size, watermark)
         if not self._h:
             raise ValueError("invalid KV block manager parameters")
-        self.num_blocks, self.block_size = num_blocks, block_size
+        self.num_blocks, self.block_size, self.state_slots = num_blocks, block_size, int(state_slots)
+        if state_slots and lib().llmctl_kv_set_state_slots(self._h, int(state_slots)) != 0:
+            raise ValueError("invalid number of state slots")
 
     def allocate(self, seq_id: int, num_tokens: int) -> bool:
         return lib().llmctl_kv_allocate(self._h, seq_id, num_tokens) == 0
@@ -71,6 +77,14 @@ class KVBlockManager:
             buf = (c_int * k)()
             k = lib().llmctl_kv_block_table(self._h, seq_id, buf, k)
         return list(buf[:k])
+
+    def state_slot(self, seq_id: int) -> int:
+        """The state slot ``seq_id`` owns (-1: none)."""
+        return lib().llmctl_kv_state_slot(self._h, seq_id)
+
+    @property
+    def free_state_slots(self) -> int:
+        return lib().llmctl_kv_free_state_slots(self._h)
 
     @property
     def free_blocks(self) -> int:

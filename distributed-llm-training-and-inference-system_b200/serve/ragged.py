@@ -19,12 +19,14 @@ from ..ops.latent_attention import ROWS_PER_TILE, TILE_WIDTHS
 @dataclass
 class Portion:
     """The next ``len(tokens)`` tokens of one sequence, which already holds ``start`` tokens in the cache; ``want`` lists
-    the offsets within ``tokens`` whose logits are asked for."""
+    the offsets within ``tokens`` whose logits are asked for.  ``state_slot``: the sequence's slot in the per-sequence
+    states of recurrent layers (-1: the model keeps none)."""
     seq_id: int
     tokens: Seq[int]
     start: int
     want: Seq[int]
     block_table: Seq[int]
+    state_slot: int = -1
 
 
 class RaggedBatch:
@@ -54,14 +56,15 @@ class RaggedBatch:
             n_out = sum(len(p.want) for p in portions)
             ntiles = tuple(sum((len(p.tokens) + w - 1) // w for p in portions) for w in self._tile_tokens)
         # int32 words: tokens(2T) | slots(2T) | out_rows(2 n_out) | positions(T) | block tables(B max_blocks) | tiles(4 n) per width
-        # | block-table row of every token(T)
-        sizes = [2 * T, 2 * T, 2 * n_out, T, B * max_blocks] + [4 * n for n in ntiles] + [T]
+        # | block-table row of every token(T) | portions(4 B)
+        sizes = [2 * T, 2 * T, 2 * n_out, T, B * max_blocks] + [4 * n for n in ntiles] + [T, 4 * B]
         offs = np.concatenate([[0], np.cumsum(sizes)])
         self._host = torch.zeros(int(offs[-1]), dtype=torch.int32, pin_memory=device.type == "cuda")
         a = self._host.numpy()
         self._h = (a[offs[0]:offs[1]].view(np.int64), a[offs[1]:offs[2]].view(np.int64), a[offs[2]:offs[3]].view(np.int64),
                    a[offs[3]:offs[4]], tuple(a[offs[5 + k]:offs[6 + k]].reshape(n, 4) for k, n in enumerate(ntiles)),
-                   a[offs[4]:offs[5]].reshape(B, max_blocks), a[offs[5 + len(ntiles)]:offs[6 + len(ntiles)]])
+                   a[offs[4]:offs[5]].reshape(B, max_blocks), a[offs[5 + len(ntiles)]:offs[6 + len(ntiles)]],
+                   a[offs[6 + len(ntiles)]:offs[7 + len(ntiles)]].reshape(B, 4))
         dev = torch.empty_like(self._host, device=device) if device.type == "cuda" else self._host
         self._dev = dev
         self.nbytes = self._host.numel() * 4
@@ -73,11 +76,14 @@ class RaggedBatch:
         self._tiles = {w: dev[offs[5 + k]:offs[6 + k]].view(ntiles[k], 4) for k, w in enumerate(TILE_WIDTHS)}
         self.block_tables = dev[offs[4]:offs[5]].view(B, max_blocks)
         self.seq_rows = dev[offs[5 + len(ntiles)]:offs[6 + len(ntiles)]]       # int32 [T]: row of block_tables per token
+        # int32 [B, 4] = (first token row, tokens, position of the first token, state slot) per portion; row b belongs to
+        # block_tables[b] and seq_rows == b (recurrent layers walk a portion's tokens from its slot's state)
+        self.portions = dev[offs[6 + len(ntiles)]:offs[7 + len(ntiles)]].view(B, 4)
         self.refill(portions)
 
     def refill(self, portions: List[Portion]) -> None:
         """Write the description of ``portions`` into the (same) buffers and copy it to the device."""
-        tokens, slots, out_rows, positions, tiles, tables, seq_rows = self._h
+        tokens, slots, out_rows, positions, tiles, tables, seq_rows, prows = self._h
         block_size = self.block_size
         if self.pad_to is not None:
             assert len(portions) <= self.pad_to[0] and all(len(p.tokens) == 1 for p in portions)
@@ -90,6 +96,7 @@ class RaggedBatch:
                 for tl in tiles:
                     tl[r] = (r, 1, r, 0)
                 out_rows[r] = r
+                prows[r] = (r, 1, 0, -1)                    # a padding row keeps no state
         t = o = 0
         ti = [0] * len(tiles)
         for b, p in enumerate(portions):
@@ -103,6 +110,7 @@ class RaggedBatch:
             slots[t:t + n] = bt[pos // block_size] * block_size + pos % block_size
             tables[b, :len(bt)] = bt
             seq_rows[t:t + n] = b
+            prows[b] = (t, n, p.start, p.state_slot)
             if self.pad_to is None:
                 for w in p.want:
                     assert 0 <= w < n

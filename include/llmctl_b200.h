@@ -245,8 +245,12 @@ int llmctl_latent_attention_t5(const void* ql, int ql_bf16, long long ql_st, lon
                                const float* freq, float mult, float scale, int H, int R, int dr, int heads_per_tile,
                                int splits, int keys_per_split, void* qfull, void* out, float* partial, void* stream);
 int llmctl_moe_tile_rows(void);
+/* correction: fp32 [E] added to the scores for the CHOICE only, or null; n_groups > 1: only experts of the keep_groups
+ * best groups (of E / n_groups neighbours each) can be chosen.  Ids >= the E given to plan / permute are identity
+ * experts. */
 int llmctl_moe_route(const float* x, const void* wr, const void* wg, int is_fp32, int tokens, int W, int E, int top,
-                     int softmax_scores, int renormalise, int* ids, float* weights, float* gate, int* counts, void* stream);
+                     int softmax_scores, int renormalise, const float* correction, int n_groups, int keep_groups, int* ids,
+                     float* weights, float* gate, int* counts, void* stream);
 /* meta: int32 [2 E + 2 + max_tiles] = { segment offsets[E] | cursors[E] | tiles | padded rows | tile -> expert }. */
 int llmctl_moe_plan(const int* counts, int E, int* meta, int max_tiles, int tile_rows, void* stream);
 int llmctl_moe_permute(const float* x, int W, const int* ids, const float* weights, int scale_input, int* meta, int E,
@@ -256,9 +260,12 @@ int llmctl_grouped_gemm(const void* A, long long lda, const void* Wt, void* out,
 /* The tcgen05 GEMM over 128-row blocks of A, block i against expert tile_expert[i]'s [N, K] matrix. */
 int llmctl_gemm_bf16_grouped(const void* A, const void* W, void* C, int max_tiles, int N, int K, long long lda,
                              long long ldc, const int* tile_expert, const int* num_tiles, int experts, void* stream);
+/* identity_in: fp32 [tokens, W], what an identity expert (pair_row < 0) returns times its weight; null without them. */
 int llmctl_moe_combine(const void* expert_out, int W, const int* pair_row, const float* weights, int top,
-                       int scale_output, const void* shared_out, const float* gate, float* y, int tokens, int is_fp32,
-                       void* stream);
+                       int scale_output, const void* shared_out, const float* gate, const float* identity_in, float* y,
+                       int tokens, int is_fp32, void* stream);
+int llmctl_gated_clamped(const void* gate_up, long long ld, void* out, int is_fp32, int rows, int F, float limit, float alpha,
+                         void* stream);
 
 /* ---- sandwich-norm layout and pooled-window attention (csrc/norm/sandwich_norm.cu, csrc/activation/xielu.cu,
  *      csrc/attention/pooled_window_attention.cu) ---- */
@@ -295,6 +302,39 @@ int llmctl_pooled_window_attention_mma(const float* q, const void* cache, const 
                                        const float* temp, const float* talk, float scale, int H, int G, int d, int e, int S,
                                        int P, int bs, int PS, void* out, int splits, int tokens, float* part_ml,
                                        float* part_o, void* stream);
+
+/* ---- parallel residual layout, differential attention, recurrent mixers (csrc/norm/parallel_norm.cu,
+ *      csrc/attention/diff_attention.cu, csrc/recurrent/gla.cu, csrc/recurrent/selective_scan.cu) ---- */
+/* Optional x[row] += add in place, then layer norm (weight, bias) of all rows or of `rows`; out32: unrounded copy or null. */
+int llmctl_layernorm_rows(float* x, const long long* rows, const float* add, const float* w, const float* b, void* out,
+                          int out_fp32, float* out32, int n, int W, float eps, void* stream);
+/* x += mult * (a + f) (+ add) in place; with w/b also the layer norm of the new rows. */
+int llmctl_parallel_residual(const void* a, int a_fp32, long long lda, const float* f, float* x, float mult, const float* add,
+                             const float* w, const float* b, void* out, int out_fp32, float* out32, int T, int W, float eps,
+                             void* stream);
+/* Rotates the first `rot` numbers of each of nq query and nk key vectors of d numbers; q -> fp32, [k | v] -> cache row. */
+int llmctl_rotary_kv_append(const void* proj, long long ld, int nq, int nk, int d, int nv, int rot, const float* freq,
+                            float mult, const int* positions, const long long* slots, float* q_out, void* cache, int tokens,
+                            int is_fp32, void* stream);
+int llmctl_diff_attention_heads_per_cta(int H, int G, int tile_tokens);
+/* Two softmax maps per head over shared values: o = a1 - lambda a2, unit RMS, * post_scale * sigmoid(gate). */
+int llmctl_diff_attention(const float* q, const void* cache, const int* block_tables, int max_blocks, const int* tiles,
+                          int ntiles, int tile_tokens, const int* positions, const void* gate, long long gate_ld, float scale,
+                          float lambda, float post_scale, float eps, int H, int G, int d, int e, int bs, void* out, int splits,
+                          float* part_ml, float* part_o, int is_fp32, void* stream);
+/* portions: int32 [n, 4] = (first token row, tokens, position of the first token, state slot). */
+int llmctl_gla_scan(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv, const void* z,
+                    long long ldz, const float* z_bias, const int* portions, int nportions, float* state, float* out, int H,
+                    int d, int e, float q_scale, float tau, int is_fp32, void* stream);
+int llmctl_gla_output(const float* o, const float* w, const void* gate, long long ldg, void* out, int tokens, int H, int e,
+                      float eps, int is_fp32, void* stream);
+int llmctl_causal_conv_silu(const void* x, long long ldx, const float* w, const float* wb, const int* portions,
+                            const int* seq_rows, const float* conv_state, void* out, int tokens, int C, int taps, int is_fp32,
+                            void* stream);
+int llmctl_selective_scan(const void* u, const void* bc, long long ldbc, int off_b, int off_c, const void* dtp, long long lddt,
+                          const float* dt_bias, const float* A, const float* D, const void* z, long long ldz, const void* x,
+                          long long ldx, const int* portions, int nportions, float* state, float* conv_state, void* out, int C,
+                          int N, int taps, int is_fp32, void* stream);
 
 #ifdef __cplusplus
 }

@@ -32,6 +32,12 @@ int llmctl_kv_can_allocate(void* kv, int num_tokens);
 /* Share parent's blocks with child (prefix sharing).  If the last block is partially filled it must be
  * copied before the child appends: returns 1 and sets *cow_src / *cow_dst, else 0; -1 on error. */
 int llmctl_kv_fork(void* kv, long long parent, long long child, int* cow_src, int* cow_dst);
+/* State slots for models with recurrent layers: `num_slots` fixed-size per-sequence states beside the pages (call
+ * before any sequence exists; 0 = none).  A sequence takes a slot at its first allocation, which fails (-1) when no
+ * slot is free, and returns it in llmctl_kv_free.  Fork is refused while slots are in use. */
+int llmctl_kv_set_state_slots(void* kv, int num_slots);
+int llmctl_kv_state_slot(void* kv, long long seq_id);       /* -1 if unknown or none */
+int llmctl_kv_free_state_slots(void* kv);
 
 /* ---------------- batch scheduler ---------------- */
 enum { LLMCTL_SCHED_DYNAMIC = 0, LLMCTL_SCHED_SIMPLE = 1, LLMCTL_SCHED_VLLM_LIKE = 2 };
