@@ -77,14 +77,16 @@ gla_scan_kernel(const GlaParams p) {
   fetch(t0);
   for (int i = 0; i < n; ++i) {
     const float cq = rowok ? nq * p.q_scale : 0.f, ck = rowok ? nk : 0.f;
-    const float ca = rowok ? expf(log_sigmoid(nz + zb) * p.inv_tau) : 0.f;
+    // the decay minus one: a is close to 1 for slow channels, and S + (a - 1) S keeps it exact to ~1e-10 instead of the
+    // ulp of 1 that a rounded factor carries (a state with a memory of thousands of tokens would accumulate that)
+    const float ca = rowok ? expm1f(log_sigmoid(nz + zb) * p.inv_tau) : -1.f;
     const float cv = nv;
     if (i + 1 < n) fetch(t0 + i + 1);
     float o = 0.f;
 #pragma unroll
     for (int j = 0; j < RPT; ++j) {
       const float aj = __shfl_sync(0xffffffffu, ca, j), kj = __shfl_sync(0xffffffffu, ck, j), qj = __shfl_sync(0xffffffffu, cq, j);
-      S[j] = aj * S[j] + kj * cv;
+      S[j] = fmaf(aj, S[j], fmaf(kj, cv, S[j]));
       o += qj * S[j];
     }
     part[i & 1][warp][lane] = o;

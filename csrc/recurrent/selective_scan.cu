@@ -16,7 +16,8 @@
 //       portion and walks its tokens with the next token's operands in flight; the lanes' partial sums meet by two
 //       shuffles.  At the end the CTA stores S and the portion's last taps-1 raw inputs (shifting in stored ones when
 //       the portion is shorter).  A portion at position 0 starts from zeros whatever its slot holds.
-// Step sizes, exponentials, state and sums are fp32; x, z, B, C and dtp are read in the projections' type.
+// The decay is applied as S + expm1(dt A) S.  Step sizes, exponentials, state and sums are fp32; x, z, B, C and dtp are
+// read in the projections' type.
 // Reference: none (the reference has no model code).
 #include "../common/dtype.cuh"
 
@@ -120,7 +121,9 @@ selective_scan_kernel(const ScanParams p) {
     float y = 0.f;
 #pragma unroll
     for (int k = 0; k < SPT; ++k) {
-      S[k] = expf(dt * A[k]) * S[k] + du * B[k];
+      // exp(dt A) is close to 1 for slow channels: S + expm1(dt A) S keeps the decay exact to ~1e-10 instead of the
+      // ulp of 1 that a rounded factor carries, which a state with a memory of thousands of tokens would accumulate
+      S[k] = fmaf(expm1f(dt * A[k]), S[k], fmaf(du, B[k], S[k]));
       y += S[k] * Cc[k];
     }
     y += __shfl_xor_sync(0xffffffffu, y, 1);
