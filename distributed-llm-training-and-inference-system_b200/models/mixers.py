@@ -314,7 +314,9 @@ class DifferentialAttention(nn.Module):
         q = dops.rotary_kv_append(p, 2 * s.heads, 2 * s.kv_heads, s.dim, self.nv, s.rot_dims, self.rot_freq, self.rot_mult,
                                   batch.positions, batch.slots, cache)
         gate = p[:, self.nq + self.nk + self.nv:] if s.head_gate else None
-        o = dops.diff_attention(q, cache, batch.block_tables, batch.tiles(self.TILE_TOKENS), 1 if batch.decode_only else self.TILE_TOKENS,
+        # prompt portions: tiles of 128 tokens on the tensor-core kernel, of 16 on the FMA kernel; decoded tokens: one each
+        width = dops.tile_width(cache.dtype, s.heads, s.kv_heads, s.dim, s.vdim, q.is_cuda, batch.decode_only)
+        o = dops.diff_attention(q, cache, batch.block_tables, batch.tiles(width), 1 if batch.decode_only else width,
                                 batch.positions, gate, s.scale, self.lam, 1.0 - s.diff, self.eps, s.heads, s.kv_heads, s.dim, s.vdim,
                                 batch.block_size, h.dtype, max_context=batch.max_context)
         return ops.linear(o, self.w_o)

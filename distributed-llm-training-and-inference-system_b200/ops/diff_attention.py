@@ -10,6 +10,7 @@ CPU tensors run the PyTorch restatement below (CPU tests); on a GPU a missing ke
 Reference: none — the reference has no attention code (reference llmctl/serve/server.py:199-204)."""
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -23,10 +24,13 @@ native.register_signature("llmctl_rotary_kv_append", [c_void_p, c_ll, c_int, c_i
 native.register_signature("llmctl_diff_attention_heads_per_cta", [c_int, c_int, c_int])
 native.register_signature("llmctl_diff_attention", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_ll,
                                                      c_float, c_float, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                                     c_int, c_void_p, c_void_p, c_int, c_void_p])
+                                                     c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+native.register_signature("llmctl_diff_attention_mma_ok", [c_int, c_int, c_int, c_int, c_int])
 native._KERNELS_PER_CALL["llmctl_diff_attention_heads_per_cta"] = 0
+native._KERNELS_PER_CALL["llmctl_diff_attention_mma_ok"] = 0
 
-TILE_TOKENS = 16        # widest query tile of the attention kernel
+TILE_TOKENS = 16        # widest query tile of the FMA attention kernel
+TILE_TOKENS_MMA = 128   # widest query tile of the tensor-core kernel (8 warps x 16 rows)
 
 
 def rotary_kv_append(proj: torch.Tensor, nq: int, nk: int, d: int, nv: int, rot: int, freq: torch.Tensor, mult: float,
@@ -54,6 +58,21 @@ def rotary_kv_append(proj: torch.Tensor, nq: int, nk: int, d: int, nv: int, rot:
     return q.reshape(T, Nq)
 
 
+def uses_tensor_cores(dtype: torch.dtype, H: int, G: int, d: int, e: int, tile_tokens: int) -> bool:
+    """bf16 caches whose sizes fit the mma.sync kernel (d a multiple of 16, e a multiple of 8 up to 128, shared memory)
+    run on it; fp32 and other sizes run the FMA kernel.  Same rule as llmctl_diff_attention_mma_ok."""
+    if dtype != torch.bfloat16 or not native.has_symbol("llmctl_diff_attention_mma_ok"):
+        return False
+    if os.environ.get("LLMCTL_DIFF_ATTENTION", "") == "fma":           # ablation switch: the FMA kernel for bf16 too
+        return False
+    return bool(native.lib().llmctl_diff_attention_mma_ok(H, G, d, e, tile_tokens))
+
+
+def tile_width(dtype: torch.dtype, H: int, G: int, d: int, e: int, cuda: bool, decode_only: bool) -> int:
+    """Width of the ragged batch's query tiles the attention wants for a batch with prompt portions."""
+    return TILE_TOKENS_MMA if cuda and not decode_only and uses_tensor_cores(dtype, H, G, d, e, TILE_TOKENS_MMA) else TILE_TOKENS
+
+
 def heads_per_cta(H: int, G: int, tile_tokens: int) -> int:
     return int(native.lib().llmctl_diff_attention_heads_per_cta(H, G, tile_tokens))
 
@@ -67,10 +86,12 @@ def key_splits(ctas: int, max_context: int, sms: int = 148) -> int:
 def diff_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor, tile_tokens: int,
                    positions: torch.Tensor, gate: Optional[torch.Tensor], scale: float, lam: float, post_scale: float, eps: float,
                    H: int, G: int, d: int, e: int, block_size: int, out_dtype: torch.dtype, max_context: int = 0,
-                   splits: int = 0) -> torch.Tensor:
+                   splits: int = 0, tensor_cores: bool = True) -> torch.Tensor:
     """q: fp32 [T, H*2*d] (rotated); tiles: int32 [n, 4] = (first token row, tokens <= tile_tokens, block-table row, 0),
     the tokens of a tile being consecutive positions of one sequence; gate: [T, H] pre-sigmoid (a view with unit column
-    stride) or None.  ``max_context`` (longest context in the batch) lets the kernel split the keys when tiles are few.
+    stride) or None.  ``tile_tokens``: 1 (every tile is one decoded token), up to 16, or — where ``uses_tensor_cores`` —
+    up to 128.  ``tensor_cores`` False forces the FMA kernel.  ``max_context`` (longest context in the batch) lets the
+    kernel split the keys when tiles are few.
     Returns [T, H e] in ``out_dtype``."""
     T = q.shape[0]
     bs = block_size
@@ -79,15 +100,20 @@ def diff_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Ten
         assert gate is None or (gate.stride(1) == 1 and gate.dtype == out_dtype)
         out = torch.empty(T, H * e, dtype=out_dtype, device=q.device)
         n = tiles.shape[0]
-        hb = heads_per_cta(H, G, tile_tokens)
-        if not splits:
-            splits = key_splits(n * (H // hb), max_context)
+        mma = tensor_cores and uses_tensor_cores(cache.dtype, H, G, d, e, tile_tokens)
+        assert mma or tile_tokens <= TILE_TOKENS
+        if mma and tile_tokens > 1:
+            hb, splits = 1, 1               # prompt tiles fill the tensor-core kernel's CTAs by themselves
+        else:
+            hb = heads_per_cta(H, G, tile_tokens)
+            if not splits:
+                splits = key_splits(n * (H // hb), max_context)
         part_ml = torch.empty(n * (H // hb) * splits * 64, dtype=torch.float32, device=q.device) if splits > 1 else None
         part_o = torch.empty(n * (H // hb) * splits * 32 * e, dtype=torch.float32, device=q.device) if splits > 1 else None
         native.call("llmctl_diff_attention", q.data_ptr(), cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
                     tiles.data_ptr(), n, int(tile_tokens), positions.data_ptr(), native.ptr(gate), gate.stride(0) if gate is not None else 0,
                     float(scale), float(lam), float(post_scale), float(eps), H, G, d, e, bs, out.data_ptr(), int(splits),
-                    native.ptr(part_ml), native.ptr(part_o), _is32(cache), native.stream_ptr())
+                    native.ptr(part_ml), native.ptr(part_o), _is32(cache), int(mma), native.stream_ptr())
         return out
     out = torch.zeros(T, H, e, dtype=torch.float32)
     flat = cache.view(-1, cache.shape[-1]).float()

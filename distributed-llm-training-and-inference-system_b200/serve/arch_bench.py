@@ -1,8 +1,8 @@
-"""Serving throughput of a ragged-batch design (Nafazen, Teluzen) beside the GPT/LLaMA family at equal parameter count:
+"""Serving throughput of a ragged-batch design (Nafazen, Teluzen, Namisun) beside the GPT/LLaMA family at equal parameter count:
 prefill and decode tokens/s through ``InferenceEngine.generate`` (the scheduler, block manager and step function a
 user gets), random weights, a few layer sizes that resemble real models; plus device-timed runs of the design's own
 attention and expert kernels against the measured roofline, next to the GPT family's like kernels.
-``bench.py --arch-compare nafazen|teluzen`` prints the result as one JSON line.
+``bench.py --arch-compare nafazen|teluzen|namisun`` prints the result as one JSON line.
 
 Reference: the reference's serving benchmark is ``llmctl bench e2e`` (reference llmctl/cli/commands/bench.py:98-160)."""
 from __future__ import annotations
@@ -32,6 +32,18 @@ TELUZEN_SIZES: Dict[str, Dict[str, Any]] = {
 }
 
 
+NAMISUN_SIZES: Dict[str, Dict[str, Any]] = {
+    # 6 layers: scan, linear attention, differential attention, twice; a mixture of 6 experts + 2 identity experts in every
+    # layer.  No loop here: a looped range adds compute without parameters, and the GPT beside it has equal parameters.
+    "w1024": dict(width=1024, vocab=32000, pattern="MGAMGA", moe="1", loop=None, heads=8, kv_heads=2, dim=64, vdim=128, rot_dims=64,
+                  rot_factor=8.0, gla_heads=8, gla_dim=64, gla_vdim=128, decay_rank=16, inner=2048, state=16, dt_rank=64, conv=4,
+                  experts=6, identity=2, top=2, groups=(4, 2), ff=1024, limit=7.0),
+    "w2048": dict(width=2048, vocab=32000, pattern="MGAMGA", moe="1", loop=None, heads=16, kv_heads=4, dim=64, vdim=128, rot_dims=64,
+                  rot_factor=8.0, gla_heads=16, gla_dim=64, gla_vdim=128, decay_rank=16, inner=4096, state=16, dt_rank=128, conv=4,
+                  experts=6, identity=2, top=2, groups=(4, 2), ff=2048, limit=7.0),
+}
+
+
 def _peaks() -> Dict[str, float]:
     p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
     try:
@@ -45,7 +57,8 @@ def _gpt_equal(ncfg, params: int):
     """A GPT configuration of the same width, depth, heads and vocabulary whose feed-forward width is chosen so that
     the parameter counts match."""
     from ..models.config import ModelConfig
-    L, W, H = len(ncfg.layers), ncfg.width, ncfg.layers[0].mixer.heads
+    L, W = len(ncfg.layers), ncfg.width
+    H = next(l.mixer.heads for l in ncfg.layers if hasattr(l.mixer, "heads"))
     hd = W // H
     fixed = 2 * ncfg.vocab_size * W + L * (4 * W * H * hd + 2 * W) + W
     ffn = max(256, int((params - fixed) / (3 * W * L)) // 128 * 128)
@@ -213,6 +226,101 @@ def _teluzen_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str,
     return res
 
 
+def _namisun_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
+    """The design's own kernels in isolation (bf16, L2 flushed before every call): differential attention, the gated
+    linear attention scan and the selective scan as prefill (2 x 2048 tokens) and as decode (32 sequences; context 4096
+    for the attention), the rotation + cache append, the fused residual + layer norm, and the mixture-of-experts layer
+    on 4096 tokens."""
+    from ..ops import diff_attention as DA
+    from ..ops import elementwise as E
+    from ..ops import moe as M
+    from ..ops import native
+    from ..ops import recurrent as R
+    from ..ops.elementwise import rope_frequencies
+    from .ragged import Portion, RaggedBatch
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    H, G, d, e = size["heads"], size["kv_heads"], size["dim"], size["vdim"]
+    gH, gd, ge = size["gla_heads"], size["gla_dim"], size["gla_vdim"]
+    C, N, Rk, taps = size["inner"], size["state"], size["dt_rank"], size["conv"]
+    W = size["width"]
+    bs, res = 64, {}
+    Wc = G * (2 * d + e)
+    freq, mult = rope_frequencies(size["rot_dims"], 10000.0, {"factor": size["rot_factor"]})
+    freq = freq.to(dev)
+    for name, nseq, ctx, new in (("prefill", 2, 2048, 2048), ("decode", 32, 4096, 1)):
+        per = (ctx + bs - 1) // bs
+        cache = torch.randn(nseq * per, bs, Wc, device=dev).to(bf)
+        ps = [Portion(i, [0] * new, ctx - new, [], list(range(i * per, (i + 1) * per)), i) for i in range(nseq)]
+        b = RaggedBatch(ps, bs, dev)
+        T = b.num_tokens
+        q = torch.randn(T, H * 2 * d, device=dev)
+        gate = torch.randn(T, H, device=dev).to(bf)
+        tile_tokens = 1 if new == 1 else 16
+        t = _time_flushed(lambda: DA.diff_attention(q, cache, b.block_tables, b.tiles(16), tile_tokens, b.positions, gate, d ** -0.5, 0.5, 0.7,
+                                                    1e-5, H, G, d, e, bs, bf, max_context=b.max_context))
+        pairs = nseq * sum(i + 1 for i in range(ctx - new, ctx))                  # visible (query, key) pairs per head
+        flops = 2.0 * H * pairs * (2 * d + 2 * e)                                 # two score maps, two weight x value products
+        bytes_ = nseq * ctx * Wc * 2 + T * H * (2 * d * 4 + e * 2)
+        res[f"diff_attention_{name}"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "gbs": bytes_ / t / 1e9,
+                                         "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"],
+                                         "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"],
+                                         "tensor_cores": DA.uses_tensor_cores(bf, H, G, d, e, tile_tokens) if hasattr(DA, "uses_tensor_cores") else False}
+        if new > 1:
+            proj = torch.randn(T, H * 2 * d + Wc + H, device=dev).to(bf)
+            t = _time_flushed(lambda: DA.rotary_kv_append(proj, 2 * H, 2 * G, d, G * e, size["rot_dims"], freq, mult, b.positions, b.slots, cache))
+            bytes_ = T * ((H * 2 * d + Wc) * 2 + H * 2 * d * 4 + Wc * 2)
+            res["rotary_kv_append_prefill"] = {"ms": t * 1e3, "gbs": bytes_ / t / 1e9, "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
+        # gated linear attention: the scan reads q, k, v, z and writes fp32 outputs; a decode step moves the whole state twice
+        nk, nv = gH * gd, gH * ge
+        p = torch.randn(T, 2 * nk + nv, device=dev).to(bf)
+        z = torch.randn(T, nk, device=dev).to(bf)
+        zb = torch.rand(nk, device=dev) * 4
+        state = torch.zeros(nseq, gH, gd, ge, device=dev)
+        t = _time_flushed(lambda: R.gla_scan(p[:, :nk], p[:, nk:2 * nk], p[:, 2 * nk:], z, zb, b.portions, state, gH, gd, ge, gd ** -0.5, 16.0))
+        bytes_ = T * ((3 * nk + nv) * 2 + nv * 4) + 2 * state.numel() * 4
+        flops = 4.0 * T * gH * gd * ge
+        res[f"gla_scan_{name}"] = {"ms": t * 1e3, "gbs": bytes_ / t / 1e9, "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"],
+                                   "fp32_tflops": flops / t / 1e12}
+        # selective scan
+        xz = torch.randn(T, 2 * C, device=dev).to(bf)
+        u = torch.randn(T, C, device=dev).to(bf)
+        bc = torch.randn(T, Rk + 2 * N, device=dev).to(bf)
+        dtp = torch.randn(T, C, device=dev).to(bf)
+        dtb, A, D = torch.randn(C, device=dev) - 1.0, -torch.exp(torch.randn(C, N, device=dev)), torch.randn(C, device=dev)
+        sst, cst = torch.zeros(nseq, C, N, device=dev), torch.zeros(nseq, taps - 1, C, device=dev)
+        t = _time_flushed(lambda: R.selective_scan(u, bc, Rk, Rk + N, dtp, dtb, A, D, xz[:, C:], xz[:, :C], b.portions, sst, cst))
+        bytes_ = T * (4 * C * 2 + 2 * N * 2) + 2 * sst.numel() * 4
+        res[f"selective_scan_{name}"] = {"ms": t * 1e3, "gbs": bytes_ / t / 1e9, "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"],
+                                         "exp_per_s_e12": T * C * N / t / 1e12}
+        if new > 1:
+            cw, cb = torch.randn(C, taps, device=dev), torch.randn(C, device=dev)
+            t = _time_flushed(lambda: R.causal_conv_silu(xz[:, :C], cw, cb, b.portions, b.seq_rows, cst))
+            bytes_ = T * C * 4
+            res["causal_conv_prefill"] = {"ms": t * 1e3, "gbs": bytes_ / t / 1e9, "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
+            x = torch.randn(T, W, device=dev)
+            a, f = torch.randn(T, W, device=dev).to(bf), torch.randn(T, W, device=dev)
+            w1, b1 = torch.ones(W, device=dev), torch.zeros(W, device=dev)
+            t = _time_flushed(lambda: E.parallel_residual(a, f, x, 0.5, 1e-5, bf, w1, b1, want_fp32=True))
+            bytes_ = T * W * (2 + 4 + 4 + 4 + 2 + 4)
+            res["parallel_residual_norm_prefill"] = {"ms": t * 1e3, "gbs": bytes_ / t / 1e9, "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
+    E_, ident, top, F = size["experts"], size["identity"], size["top"], size["ff"]
+    T = 4096
+    x = torch.randn(T, W, device=dev)
+    wr = torch.randn(E_ + ident, W, device=dev).to(bf)
+    corr = torch.randn(E_ + ident, device=dev) * 0.01
+    wgu = (torch.randn(E_, 2 * F, W, device=dev) / W ** 0.5).to(bf)
+    wd = (torch.randn(E_, W, F, device=dev) / F ** 0.5).to(bf)
+    t = _time(lambda: M.moe_ffn(x, bf, wr, wgu, wd, top, scale_input=False, softmax=True, renormalise=True, correction=corr,
+                                groups=size["groups"], clamp=(size["limit"], 1.702)), 5)
+    flops = 2.0 * T * top * 3 * F * W * E_ / (E_ + ident)          # about ident / (E + ident) of the choices are identity experts
+    res["moe_ffn_4096_tokens"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"]}
+    gsize = dict(size, expert_ff=F)
+    res.update(_gpt_kernels(gsize, peaks))
+    res["native_launches"] = native.launch_count
+    return res
+
+
 def _gpt_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
     """The GPT family's like kernels at like sizes: causal flash attention over the same 2 x 2048 tokens, paged decode
     attention over the same 32 contexts of 4096 (head size 128 for both), and the SwiGLU feed-forward's two GEMMs on
@@ -253,6 +361,9 @@ def run(which: str = "nafazen", sizes: List[str] | None = None, prompt_len: int 
     elif which == "teluzen":
         from ..models.teluzen import TeluzenConfig as Config, example_config
         table, kernels = TELUZEN_SIZES, _teluzen_kernels
+    elif which == "namisun":
+        from ..models.namisun import NamisunConfig as Config, example_config
+        table, kernels = NAMISUN_SIZES, _namisun_kernels
     else:
         raise ValueError(f"no architecture comparison for {which!r}")
     peaks = _peaks()

@@ -321,7 +321,8 @@ int llmctl_diff_attention_heads_per_cta(int H, int G, int tile_tokens);
 int llmctl_diff_attention(const float* q, const void* cache, const int* block_tables, int max_blocks, const int* tiles,
                           int ntiles, int tile_tokens, const int* positions, const void* gate, long long gate_ld, float scale,
                           float lambda, float post_scale, float eps, int H, int G, int d, int e, int bs, void* out, int splits,
-                          float* part_ml, float* part_o, int is_fp32, void* stream);
+                          float* part_ml, float* part_o, int is_fp32, int use_mma, void* stream);
+int llmctl_diff_attention_mma_ok(int H, int G, int d, int e, int tile_tokens);
 /* portions: int32 [n, 4] = (first token row, tokens, position of the first token, state slot). */
 int llmctl_gla_scan(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv, const void* z,
                     long long ldz, const float* z_bias, const int* portions, int nportions, float* state, float* out, int H,

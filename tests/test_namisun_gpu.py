@@ -57,7 +57,8 @@ def test_mixture_kernels(cuda_device, experts, identity, top, groups, W, Ff):
 
 
 @pytest.mark.parametrize("H,G,d,e,n,far,bs", [(4, 2, 8, 12, 45, 3, 16), (2, 2, 6, 5, 133, 15, 16), (3, 1, 4, 7, 64, 0, 64), (6, 3, 10, 34, 19, 8, 8),
-                                              (8, 2, 32, 72, 300, 63, 64), (4, 1, 128, 256, 70, 64, 64), (16, 1, 16, 130, 40, 7, 16)])
+                                              (8, 2, 32, 72, 300, 63, 64), (4, 1, 128, 256, 70, 64, 64), (16, 1, 16, 130, 40, 7, 16),
+                                              (4, 4, 16, 8, 259, 127, 16), (6, 2, 64, 128, 257, 128, 64), (32, 2, 32, 40, 130, 31, 8)])
 def test_differential_attention_kernels(cuda_device, H, G, d, e, n, far, bs):
     """Prompt tiles, single-token tiles with several heads per CTA, and key slices, against the oracle; a far key
     dominates the first map of the last query."""
@@ -73,14 +74,24 @@ def test_differential_attention_kernels(cuda_device, H, G, d, e, n, far, bs):
     qg = q.reshape(n, -1).to(cuda_device)
     t16 = torch.tensor([[s, min(16, n - s), 0, 0] for s in range(0, n, 16)], dtype=torch.int32, device=cuda_device)
     t1 = torch.tensor([[s, 1, 0, 0] for s in range(n)], dtype=torch.int32, device=cuda_device)
+    t128 = torch.tensor([[s, min(128, n - s), 0, 0] for s in range(0, n, 128)], dtype=torch.int32, device=cuda_device)
     for dt, tol in ((torch.float32, 3e-5), (torch.bfloat16, 6e-2)):
         cg, gg = cache.to(dt).to(cuda_device), gate.to(dt).to(cuda_device)
-        for tiles, width, splits in ((t16, 16, 1), (t1, 1, 1), (t16, 16, 3), (t1, 1, 4), (t1[-3:], 1, 0)):
+        cases = [(t16, 16, 1, False), (t1, 1, 1, False), (t16, 16, 3, False), (t1, 1, 4, False), (t1[-3:], 1, 0, False)]
+        if DA.uses_tensor_cores(dt, H, G, d, e, 128):
+            cases += [(t128, 128, 1, True), (t16, 16, 1, True), (t1, 1, 1, True), (t1, 1, 4, True), (t1[-3:], 1, 0, True)]
+        for tiles, width, splits, tc in cases:
             got = DA.diff_attention(qg, cg, table.to(cuda_device), tiles, width, pos, gg, scale, lam, 1.0 - diff, eps, H, G, d, e, bs, dt,
-                                    max_context=n, splits=splits)
+                                    max_context=n, splits=splits, tensor_cores=tc)
             first = int(tiles[0, 0])
             err = (got.float().cpu().view(n, H, e)[first:].double() - want[first:]).abs().max()
-            assert err < tol, (dt, width, splits, float(err))
+            assert err < tol, (dt, width, splits, tc, float(err))
+        if dt == torch.bfloat16 and DA.uses_tensor_cores(dt, H, G, d, e, 128):
+            # the tensor-core kernel keeps queries and weights as bf16 pairs: it agrees with the fp32 FMA kernel on the
+            # same bf16 cache far more closely than bf16 rounding of the output alone would explain away
+            a = DA.diff_attention(qg, cg, table.to(cuda_device), t128, 128, pos, gg, scale, lam, 1.0 - diff, eps, H, G, d, e, bs, dt, tensor_cores=True)
+            b = DA.diff_attention(qg, cg, table.to(cuda_device), t16, 16, pos, gg, scale, lam, 1.0 - diff, eps, H, G, d, e, bs, dt, tensor_cores=False)
+            assert (a.float() - b.float()).abs().max() <= 0.02 and ((a.float() - b.float()).abs() > 1e-6).float().mean() < 0.1
 
 
 @pytest.mark.parametrize("H,d,e,cuts", [(2, 8, 10, (9, 1, 1, 4)), (1, 3, 1, (2, 2, 2)), (3, 5, 33, (1, 1, 13)), (2, 70, 6, (5, 3)), (2, 130, 64, (40, 2)),
