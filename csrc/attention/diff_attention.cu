@@ -387,13 +387,21 @@ diff_attention_mma_kernel(const DiffAttnParams p, int decode) {
     k_end = min(k_begin + per, nkeys);
   }
   const int kch = (2 * d) >> 3, vch = e >> 3, chunks = kch + vch;
-  auto load_tile = [&](int stage, int k0) {
+  // cache offsets of a tile's keys are looked up (page table) one tile ahead of the copies that use them
+  __shared__ long long rowoff[2][kDmKT];
+  auto index_tile = [&](int stage, int k0) {
+    if (tid < kDmKT) {
+      const int j = k0 + tid;
+      rowoff[stage][tid] = j < k_end ? (static_cast<long long>(table[j / bs]) * bs + j % bs) * Wc : -1;
+    }
+  };
+  auto load_tile = [&](int stage) {
     for (int i = tid; i < kDmKT * chunks; i += nthreads) {
       const int kk = i / chunks, ch = i % chunks;
-      const int j = k0 + kk;
+      const long long off = rowoff[stage][kk];
       __nv_bfloat16* dst = ch < kch ? Ks + (stage * kDmKT + kk) * ldk + ch * 8 : Vs + (stage * kDmKT + kk) * ldv + (ch - kch) * 8;
-      if (j < k_end) {
-        const __nv_bfloat16* row = cache + (static_cast<long long>(table[j / bs]) * bs + j % bs) * Wc;
+      if (off >= 0) {
+        const __nv_bfloat16* row = cache + off;
         cp_async_16(dst, ch < kch ? row + g * 2 * d + ch * 8 : row + G * 2 * d + g * e + (ch - kch) * 8);
       } else {
         *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);      // a weight of 0 times stale bits could be a NaN
@@ -421,13 +429,17 @@ diff_attention_mma_kernel(const DiffAttnParams p, int decode) {
   }
 
   const int ntile = (k_end - k_begin + kDmKT - 1) / kDmKT;
-  if (ntile > 0) load_tile(0, k_begin);
+  if (ntile > 0) index_tile(0, k_begin);
+  if (ntile > 1) index_tile(1, k_begin + kDmKT);
+  __syncthreads();
+  if (ntile > 0) load_tile(0);
   cp_async_commit();
   for (int it = 0; it < ntile; ++it) {
     cp_async_wait_all();
     __syncthreads();                       // tile `it` has landed (and Q); everyone is done with the other stage
-    if (it + 1 < ntile) load_tile((it + 1) & 1, k_begin + (it + 1) * kDmKT);
+    if (it + 1 < ntile) load_tile((it + 1) & 1);
     cp_async_commit();
+    if (it + 2 < ntile) index_tile(it & 1, k_begin + (it + 2) * kDmKT);     // its last readers ran before the barrier
     const int k0 = k_begin + it * kDmKT, st = it & 1;
     if (!warp_active || k0 > warp_last) continue;
     const __nv_bfloat16* Kt = Ks + st * kDmKT * ldk;

@@ -7,10 +7,11 @@
 //     o_t = S_t^T q_t
 //     a_t = sigmoid(z_t + bias)^(1/tau) = exp(logsigmoid(z_t + bias) / tau)
 //
-//   llmctl_gla_scan   : a CTA owns (portion, head, block of 32 value columns); lane = column, warp = block of RPT key
-//       rows, whose state lives in registers for the whole portion.  Each warp loads its rows' q, k and decay logits
-//       of the next token while it works on the current one (no block-wide staging); the per-row numbers reach the
-//       lanes by shuffles; the warps' partial outputs meet in shared memory (one barrier per token, two buffers).
+//   llmctl_gla_scan   : first, fully parallel, the scaled queries, keys and decays (minus one) of the step's tokens in
+//       fp32.  Then a CTA owns (portion, head, block of 32 value columns); lane = column, warp = block of RPT key
+//       rows, whose state lives in registers for the whole portion.  The portion is walked in chunks of 16 tokens: the
+//       CTA stages a chunk's prepared numbers and values in shared memory while the previous chunk's steps run on
+//       what was staged before; a step reads its rows' numbers as broadcast float4s.  The warps' partial outputs of a chunk meet in shared memory: two barriers per chunk, none per token.
 //       A portion that starts at position 0 starts from zeros whatever its slot holds; otherwise from the slot.
 //   llmctl_gla_output : per (token, head), o / sqrt(mean(o^2) + eps) * w (w shared by the heads) times silu(gate).
 // Decay, state, outputs and the norm are fp32; q, k, v, z and the gate are read in the projections' type.
@@ -35,20 +36,49 @@ struct GlaParams {
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
+constexpr int kGlaTC = 16;      // tokens staged per chunk
+
+// work[t] = [scaled queries | keys | decay minus one] of token t in fp32, 3 * H * d numbers: everything the serial scan
+// would otherwise evaluate (the decay's three transcendentals above all) happens here, fully parallel.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gla_prepare_kernel(const GlaParams p, float* __restrict__ work, int tokens) {
+  const int nk = p.H * p.d;
+  const long long total = static_cast<long long>(tokens) * nk;
+  const T* q = static_cast<const T*>(p.q);
+  const T* k = static_cast<const T*>(p.k);
+  const T* z = static_cast<const T*>(p.z);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / nk;
+    const int c = static_cast<int>(i % nk);
+    float* w = work + t * 3 * nk + c;
+    w[0] = to_f32(q[t * p.ldq + c]) * p.q_scale;
+    w[nk] = to_f32(k[t * p.ldk + c]);
+    // the decay minus one: a is close to 1 for slow channels, and S + (a - 1) S keeps it exact to ~1e-10 instead of the
+    // ulp of 1 that a rounded factor carries (a state with a memory of thousands of tokens would accumulate that)
+    w[2 * nk] = expm1f(log_sigmoid(to_f32(z[t * p.ldz + c]) + (p.z_bias ? p.z_bias[c] : 0.f)) * p.inv_tau);
+  }
+}
+
 template <typename T, int RPT>
 __global__ void __launch_bounds__(256)
-gla_scan_kernel(const GlaParams p) {
-  __shared__ float part[2][8][32];
-  const int H = p.H, d = p.d, e = p.e;
+gla_scan_kernel(const GlaParams p, const float* __restrict__ work) {
+  constexpr int TC = kGlaTC, NTR = RPT / 2;      // (q, k, decay) triples a thread stages per chunk: TC * dpad / threads
+  constexpr int TSTEP = 32 / RPT;                // tokens between a thread's staging elements
+  extern __shared__ __align__(16) float gla_smem[];
+  const int H = p.H, d = p.d, e = p.e, nk = H * d;
   const int* pt = p.portions + blockIdx.x * 4;
   const int t0 = pt[0], n = pt[1], pos0 = pt[2], slot = pt[3];
   if (n <= 0) return;
   const int h = blockIdx.y, col = blockIdx.z * 32 + (threadIdx.x & 31);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const int row0 = warp * RPT;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5, nthreads = blockDim.x;
+  const int dpad = nwarps * RPT, row0 = warp * RPT;
   const bool colok = col < e;
-  const int myrow = row0 + lane;                         // the key row whose q / k / decay this lane fetches
-  const bool rowok = lane < RPT && myrow < d;
+  float* sq = gla_smem;                  // [TC][dpad] scaled queries
+  float* sk = sq + TC * dpad;            // [TC][dpad] keys
+  float* sa = sk + TC * dpad;            // [TC][dpad] decay minus one
+  float* sv = sa + TC * dpad;            // [TC][32] values of this CTA's columns
+  float* part = sv + TC * 32;            // [TC][nwarps][32] partial outputs of the warps
 
   float S[RPT];
 #pragma unroll
@@ -59,43 +89,81 @@ gla_scan_kernel(const GlaParams p) {
     for (int j = 0; j < RPT; ++j)
       if (row0 + j < d) S[j] = st[static_cast<long long>(row0 + j) * e + col];
   }
-  const T* q = static_cast<const T*>(p.q);
-  const T* k = static_cast<const T*>(p.k);
   const T* v = static_cast<const T*>(p.v);
-  const T* z = static_cast<const T*>(p.z);
-  const float zb = (rowok && p.z_bias) ? p.z_bias[h * d + myrow] : 0.f;
 
-  float nq = 0.f, nk = 0.f, nz = 0.f, nv = 0.f;
-  auto fetch = [&](long long t) {
-    if (rowok) {
-      nq = to_f32(q[t * p.ldq + h * d + myrow]);
-      nk = to_f32(k[t * p.ldk + h * d + myrow]);
-      nz = to_f32(z[t * p.ldz + h * d + myrow]);
-    }
-    nv = colok ? to_f32(v[t * p.ldv + h * e + col]) : 0.f;
-  };
-  fetch(t0);
-  for (int i = 0; i < n; ++i) {
-    const float cq = rowok ? nq * p.q_scale : 0.f, ck = rowok ? nk : 0.f;
-    // the decay minus one: a is close to 1 for slow channels, and S + (a - 1) S keeps it exact to ~1e-10 instead of the
-    // ulp of 1 that a rounded factor carries (a state with a memory of thousands of tokens would accumulate that)
-    const float ca = rowok ? expm1f(log_sigmoid(nz + zb) * p.inv_tau) : -1.f;
-    const float cv = nv;
-    if (i + 1 < n) fetch(t0 + i + 1);
-    float o = 0.f;
+  // staging: this thread's element i of a chunk is (token stok + i * TSTEP, key row srow); nthreads is a multiple of dpad
+  const int srow = tid % dpad, stok = tid / dpad;
+  const bool srow_ok = srow < d;
+  const float* wbase = work + static_cast<long long>(t0) * 3 * nk + h * d + srow;
+  // values: element (token tid / 32 + j * nwarps, column lane)
+  float rq[NTR], rk[NTR], ra[NTR], rv[TC];
+  auto fetch = [&](int c0) {
 #pragma unroll
-    for (int j = 0; j < RPT; ++j) {
-      const float aj = __shfl_sync(0xffffffffu, ca, j), kj = __shfl_sync(0xffffffffu, ck, j), qj = __shfl_sync(0xffffffffu, cq, j);
-      S[j] = fmaf(aj, S[j], fmaf(kj, cv, S[j]));
-      o += qj * S[j];
+    for (int i = 0; i < NTR; ++i) {
+      const int tok = c0 + stok + i * TSTEP;
+      const bool ok = srow_ok && tok < n;
+      const float* w = wbase + static_cast<long long>(tok) * 3 * nk;
+      rq[i] = ok ? w[0] : 0.f;
+      rk[i] = ok ? w[nk] : 0.f;
+      ra[i] = ok ? w[2 * nk] : -1.f;               // rows beyond d keep a zero state
     }
-    part[i & 1][warp][lane] = o;
+#pragma unroll
+    for (int j = 0; j < TC; ++j) {
+      const int tok = warp + j * nwarps;
+      if (tok < TC) rv[j] = (colok && c0 + tok < n) ? to_f32(v[static_cast<long long>(t0 + c0 + tok) * p.ldv + h * e + col]) : 0.f;
+    }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int i = 0; i < NTR; ++i) {
+      const int idx = (stok + i * TSTEP) * dpad + srow;
+      sq[idx] = rq[i];
+      sk[idx] = rk[i];
+      sa[idx] = ra[i];
+    }
+#pragma unroll
+    for (int j = 0; j < TC; ++j) {
+      const int tok = warp + j * nwarps;
+      if (tok < TC) sv[tok * 32 + lane] = rv[j];
+    }
+  };
+  fetch(0);
+  stash();
+  __syncthreads();
+  for (int c0 = 0; c0 < n; c0 += TC) {
+    const bool more = c0 + TC < n;
+    if (more) fetch(c0 + TC);                       // the next chunk's loads fly during this chunk's steps
+    const int cnt = min(TC, n - c0);
+    for (int tok = 0; tok < cnt; ++tok) {
+      const float* aq = sq + tok * dpad + row0;
+      const float* ak = sk + tok * dpad + row0;
+      const float* aa = sa + tok * dpad + row0;
+      const float vv = sv[tok * 32 + lane];
+      float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < RPT; j += 4) {
+        const float4 a4 = *reinterpret_cast<const float4*>(aa + j), k4 = *reinterpret_cast<const float4*>(ak + j);
+        const float4 q4 = *reinterpret_cast<const float4*>(aq + j);
+        S[j] = fmaf(a4.x, S[j], fmaf(k4.x, vv, S[j]));
+        S[j + 1] = fmaf(a4.y, S[j + 1], fmaf(k4.y, vv, S[j + 1]));
+        S[j + 2] = fmaf(a4.z, S[j + 2], fmaf(k4.z, vv, S[j + 2]));
+        S[j + 3] = fmaf(a4.w, S[j + 3], fmaf(k4.w, vv, S[j + 3]));
+        o0 += q4.x * S[j] + q4.z * S[j + 2];
+        o1 += q4.y * S[j + 1] + q4.w * S[j + 3];
+      }
+      part[(tok * nwarps + warp) * 32 + lane] = o0 + o1;
+    }
+    __syncthreads();                                // the chunk's partial outputs are complete, its staged rows read
+    for (int idx = tid; idx < cnt * 32; idx += nthreads) {
+      const int tok = idx >> 5, c = idx & 31;
+      if (blockIdx.z * 32 + c < e) {
+        float s = 0.f;
+        for (int w = 0; w < nwarps; ++w) s += part[(tok * nwarps + w) * 32 + c];
+        p.out[(static_cast<long long>(t0 + c0 + tok) * H + h) * e + blockIdx.z * 32 + c] = s;
+      }
+    }
+    if (more) stash();
     __syncthreads();
-    if (warp == 0 && colok) {
-      float s = 0.f;
-      for (int w = 0; w < nwarps; ++w) s += part[i & 1][w][lane];
-      p.out[(static_cast<long long>(t0 + i) * H + h) * e + col] = s;
-    }
   }
   if (st && colok) {
 #pragma unroll
@@ -129,21 +197,26 @@ gla_output_kernel(const float* __restrict__ o, const float* __restrict__ w, cons
 
 using namespace llmctl;
 
+// work: fp32 [tokens, 3 * H * d] scratch (the prepared queries, keys and decays of the step's tokens).
 LLMCTL_API int llmctl_gla_scan(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv, const void* z,
-                               long long ldz, const float* z_bias, const int* portions, int nportions, float* state, float* out,
-                               int H, int d, int e, float q_scale, float tau, int is_fp32, void* stream) {
+                               long long ldz, const float* z_bias, const int* portions, int nportions, int tokens, float* state,
+                               float* out, float* work, int H, int d, int e, float q_scale, float tau, int is_fp32, void* stream) {
   LLMCTL_BEGIN();
-  LLMCTL_REQUIRE(H > 0 && d > 0 && d <= 256 && e > 0 && tau > 0.f);
-  if (nportions == 0) return 0;
+  LLMCTL_REQUIRE(H > 0 && d > 0 && d <= 256 && e > 0 && tau > 0.f && work != nullptr);
+  if (nportions == 0 || tokens == 0) return 0;
   GlaParams p{q, k, v, z, ldq, ldk, ldv, ldz, z_bias, portions, state, out, H, d, e, q_scale, 1.f / tau};
   const dim3 grid(nportions, H, (e + 31) / 32);
   cudaStream_t s = (cudaStream_t)stream;
   const int rpt = d <= 64 ? 8 : d <= 128 ? 16 : 32;
-  const int threads = 32 * ((d + rpt - 1) / rpt);
+  const int warps = (d + rpt - 1) / rpt, threads = 32 * warps;
+  const size_t smem = sizeof(float) * kGlaTC * (3 * static_cast<size_t>(warps) * rpt + 32 + warps * 32);       // <= 42 KB
+  const long long total = static_cast<long long>(tokens) * H * d;
+  const int pgrid = static_cast<int>(total / 256 + 1 < kNumSMs * 16 ? total / 256 + 1 : kNumSMs * 16);
   LLMCTL_DISPATCH_DTYPE(is_fp32, T, {
-    if (rpt == 8) gla_scan_kernel<T, 8><<<grid, threads, 0, s>>>(p);
-    else if (rpt == 16) gla_scan_kernel<T, 16><<<grid, threads, 0, s>>>(p);
-    else gla_scan_kernel<T, 32><<<grid, threads, 0, s>>>(p);
+    gla_prepare_kernel<T><<<pgrid, 256, 0, s>>>(p, work, tokens);
+    if (rpt == 8) gla_scan_kernel<T, 8><<<grid, threads, smem, s>>>(p, work);
+    else if (rpt == 16) gla_scan_kernel<T, 16><<<grid, threads, smem, s>>>(p, work);
+    else gla_scan_kernel<T, 32><<<grid, threads, smem, s>>>(p, work);
   });
   LLMCTL_RETURN_LAST();
 }

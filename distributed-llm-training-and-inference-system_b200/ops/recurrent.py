@@ -22,8 +22,9 @@ from . import native
 from .elementwise import _is32
 
 c_void_p, c_int, c_ll, c_float = native.c_void_p, native.c_int, native.c_ll, native.c_float
-native.register_signature("llmctl_gla_scan", [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_int,
-                                               c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+native.register_signature("llmctl_gla_scan", [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int,
+                                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+native._KERNELS_PER_CALL["llmctl_gla_scan"] = 2
 native.register_signature("llmctl_gla_output", [c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
 native.register_signature("llmctl_causal_conv_silu", [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                        c_int, c_int, c_int, c_void_p])
@@ -41,9 +42,10 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
     if q.is_cuda:
         assert all(t.stride(1) == 1 and t.dtype == q.dtype for t in (q, k, v, z)) and state.dtype == torch.float32 and state.is_contiguous()
         out = torch.empty(T, H * e, dtype=torch.float32, device=q.device)
+        work = torch.empty(T, 3 * H * d, dtype=torch.float32, device=q.device)        # prepared queries, keys, decays
         native.call("llmctl_gla_scan", q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), z.data_ptr(),
-                    z.stride(0), native.ptr(z_bias), portions.data_ptr(), portions.shape[0], state.data_ptr(), out.data_ptr(), H, d, e,
-                    float(q_scale), float(tau), _is32(q), native.stream_ptr())
+                    z.stride(0), native.ptr(z_bias), portions.data_ptr(), portions.shape[0], T, state.data_ptr(), out.data_ptr(),
+                    work.data_ptr(), H, d, e, float(q_scale), float(tau), _is32(q), native.stream_ptr())
         return out
     out = torch.zeros(T, H, e, dtype=torch.float32)
     zf = z.float() + (z_bias if z_bias is not None else 0.0)

@@ -256,8 +256,9 @@ def _namisun_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str,
         T = b.num_tokens
         q = torch.randn(T, H * 2 * d, device=dev)
         gate = torch.randn(T, H, device=dev).to(bf)
-        tile_tokens = 1 if new == 1 else 16
-        t = _time_flushed(lambda: DA.diff_attention(q, cache, b.block_tables, b.tiles(16), tile_tokens, b.positions, gate, d ** -0.5, 0.5, 0.7,
+        width = DA.tile_width(bf, H, G, d, e, True, new == 1)               # the tiling the model path takes
+        tile_tokens = 1 if new == 1 else width
+        t = _time_flushed(lambda: DA.diff_attention(q, cache, b.block_tables, b.tiles(width), tile_tokens, b.positions, gate, d ** -0.5, 0.5, 0.7,
                                                     1e-5, H, G, d, e, bs, bf, max_context=b.max_context))
         pairs = nseq * sum(i + 1 for i in range(ctx - new, ctx))                  # visible (query, key) pairs per head
         flops = 2.0 * H * pairs * (2 * d + 2 * e)                                 # two score maps, two weight x value products
@@ -265,7 +266,7 @@ def _namisun_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str,
         res[f"diff_attention_{name}"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "gbs": bytes_ / t / 1e9,
                                          "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"],
                                          "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"],
-                                         "tensor_cores": DA.uses_tensor_cores(bf, H, G, d, e, tile_tokens) if hasattr(DA, "uses_tensor_cores") else False}
+                                         "tensor_cores": DA.uses_tensor_cores(bf, H, G, d, e, tile_tokens)}
         if new > 1:
             proj = torch.randn(T, H * 2 * d + Wc + H, device=dev).to(bf)
             t = _time_flushed(lambda: DA.rotary_kv_append(proj, 2 * H, 2 * G, d, G * e, size["rot_dims"], freq, mult, b.positions, b.slots, cache))

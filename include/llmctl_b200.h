@@ -325,8 +325,9 @@ int llmctl_diff_attention(const float* q, const void* cache, const int* block_ta
 int llmctl_diff_attention_mma_ok(int H, int G, int d, int e, int tile_tokens);
 /* portions: int32 [n, 4] = (first token row, tokens, position of the first token, state slot). */
 int llmctl_gla_scan(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv, const void* z,
-                    long long ldz, const float* z_bias, const int* portions, int nportions, float* state, float* out, int H,
-                    int d, int e, float q_scale, float tau, int is_fp32, void* stream);
+                    long long ldz, const float* z_bias, const int* portions, int nportions, int tokens, float* state, float* out,
+                    float* work /* fp32 [tokens, 3 H d] scratch */, int H, int d, int e, float q_scale, float tau, int is_fp32,
+                    void* stream);
 int llmctl_gla_output(const float* o, const float* w, const void* gate, long long ldg, void* out, int tokens, int H, int e,
                       float eps, int is_fp32, void* stream);
 int llmctl_causal_conv_silu(const void* x, long long ldx, const float* w, const float* wb, const int* portions,
