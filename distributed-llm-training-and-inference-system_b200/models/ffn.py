@@ -89,7 +89,10 @@ class GatedExpertMoE(nn.Module):
         with torch.no_grad():
             self.router.copy_(get(prefix + "router"))
             if self.correction is not None:
-                self.correction.copy_(get(prefix + "correction").float())
+                try:
+                    self.correction.copy_(get(prefix + "correction").float())
+                except KeyError:            # a checkpoint without the vector chooses by the plain scores
+                    self.correction.zero_()
             for e in range(E):
                 self.gate_up[e].copy_(torch.cat([get(f"{prefix}e{e}.gate"), get(f"{prefix}e{e}.up")], dim=0))
                 self.down[e].copy_(get(f"{prefix}e{e}.down"))

@@ -77,11 +77,11 @@ def heads_per_cta(H: int, G: int, tile_tokens: int) -> int:
     return int(native.lib().llmctl_diff_attention_heads_per_cta(H, G, tile_tokens))
 
 
-def key_splits(ctas: int, max_context: int, per_sm: int = 2, sms: int = 148) -> int:
+def key_splits(ctas: int, max_context: int, per_sm: int = 2, min_keys: int = 128, sms: int = 148) -> int:
     """Slices to cut every tile's keys into: with few CTAs (a decoding batch) and long contexts the keys are spread
-    over about ``per_sm`` CTAs per SM (the tensor-core kernel's decode CTAs are single warps: 8), at least 128 keys per
-    slice."""
-    return int(max(1, min(per_sm * sms // max(ctas, 1), max_context // 128, 64)))
+    over about ``per_sm`` CTAs per SM, at least ``min_keys`` keys per slice (the tensor-core kernel's decode CTAs are
+    single warps on 32-key tiles: 8 per SM, 64 keys)."""
+    return int(max(1, min(per_sm * sms // max(ctas, 1), max_context // min_keys, 64)))
 
 
 def diff_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor, tile_tokens: int,
@@ -108,7 +108,7 @@ def diff_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Ten
         else:
             hb = heads_per_cta(H, G, tile_tokens)
             if not splits:
-                splits = key_splits(n * (H // hb), max_context, 8 if mma else 2)
+                splits = key_splits(n * (H // hb), max_context, 8 if mma else 2, 64 if mma else 128)
         part_ml = torch.empty(n * (H // hb) * splits * 64, dtype=torch.float32, device=q.device) if splits > 1 else None
         part_o = torch.empty(n * (H // hb) * splits * 32 * e, dtype=torch.float32, device=q.device) if splits > 1 else None
         native.call("llmctl_diff_attention", q.data_ptr(), cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
