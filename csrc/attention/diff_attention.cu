@@ -650,7 +650,8 @@ static int launch_diff_attention(const DiffAttnParams& p, int ntiles, size_t sme
   if (p.e <= 32) LLMCTL_DA_LAUNCH(1);
   else if (p.e <= 64) LLMCTL_DA_LAUNCH(2);
   else if (p.e <= 128) LLMCTL_DA_LAUNCH(4);
-  else LLMCTL_DA_LAUNCH(8);
+  else if (p.e <= 256) LLMCTL_DA_LAUNCH(8);
+  else LLMCTL_DA_LAUNCH(16);
 #undef LLMCTL_DA_LAUNCH
   return 0;
 }
@@ -663,7 +664,7 @@ LLMCTL_API int llmctl_diff_attention(const float* q, const void* cache, const in
                                      float scale, float lambda, float post_scale, float eps, int H, int G, int d, int e, int bs,
                                      void* out, int splits, float* part_ml, float* part_o, int is_fp32, int use_mma, void* stream) {
   LLMCTL_BEGIN();
-  LLMCTL_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0 && e <= 256 && bs > 0 && tile_tokens >= 1);
+  LLMCTL_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0 && e <= 512 && bs > 0 && tile_tokens >= 1);
   LLMCTL_REQUIRE(splits >= 1 && (splits == 1 || (part_ml != nullptr && part_o != nullptr)));
   if (ntiles == 0) return 0;
   if (use_mma) {

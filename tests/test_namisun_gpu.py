@@ -58,7 +58,7 @@ def test_mixture_kernels(cuda_device, experts, identity, top, groups, W, Ff):
 
 @pytest.mark.parametrize("H,G,d,e,n,far,bs", [(4, 2, 8, 12, 45, 3, 16), (2, 2, 6, 5, 133, 15, 16), (3, 1, 4, 7, 64, 0, 64), (6, 3, 10, 34, 19, 8, 8),
                                               (8, 2, 32, 72, 300, 63, 64), (4, 1, 128, 256, 70, 64, 64), (16, 1, 16, 130, 40, 7, 16),
-                                              (4, 4, 16, 8, 259, 127, 16), (6, 2, 64, 128, 257, 128, 64), (32, 2, 32, 40, 130, 31, 8)])
+                                              (4, 4, 16, 8, 259, 127, 16), (6, 2, 64, 128, 257, 128, 64), (32, 2, 32, 40, 130, 31, 8), (2, 1, 8, 300, 40, 5, 16)])
 def test_differential_attention_kernels(cuda_device, H, G, d, e, n, far, bs):
     """Prompt tiles, single-token tiles with several heads per CTA, and key slices, against the oracle; a far key
     dominates the first map of the last query."""
