@@ -152,6 +152,30 @@ def test_selective_scan_kernels(cuda_device, C, N, R_, taps, cuts):
         assert torch.allclose(conv_state[1].cpu(), torch.cat([torch.zeros(taps - 1, C), x])[-(taps - 1):])
 
 
+@pytest.mark.parametrize("N", [17, 40])
+def test_selective_scan_many_portions(cuda_device, N):
+    """Enough portions to fill the GPU: the scan takes its 4-lanes-per-channel layout for any state count; every portion
+    against the oracle, each in its own slot."""
+    from llmctl_b200.ops import recurrent as R
+    torch.manual_seed(9)
+    C, R_, taps, nport, n = 320, 3, 3, 30, 5
+    T = nport * n
+    x, z, u = torch.randn(T, C), torch.randn(T, C), torch.randn(T, C)
+    A, D, dtb = -torch.exp(torch.randn(C, N) - 1.0), torch.randn(C), torch.randn(C) - 1.0
+    bc, dtp = torch.randn(T, R_ + 2 * N), torch.randn(T, C)
+    dt = torch.nn.functional.softplus(dtp.double() + dtb.double())
+    g = lambda t: t.to(cuda_device)    # noqa: E731
+    state, conv_state = torch.randn(nport, C, N, device=cuda_device), torch.randn(nport, taps - 1, C, device=cuda_device)
+    pt = torch.tensor([[i * n, n, 0, nport - 1 - i] for i in range(nport)], dtype=torch.int32, device=cuda_device)
+    got = R.selective_scan(g(u), g(bc), R_, R_ + N, g(dtp), g(dtb), g(A), g(D), g(z), g(x), pt, state, conv_state).cpu().double()
+    for i in range(nport):
+        sl = slice(i * n, (i + 1) * n)
+        want = oracle.selective_recurrence(u[sl].double(), dt[sl], A.double(), bc[sl, R_:R_ + N].double(), bc[sl, R_ + N:].double(), D.double())
+        want = want * oracle.silu(z[sl].double())
+        assert (got[sl] - want).abs().max() < 1e-5 * want.abs().max() + 2e-5, f"portion {i}"
+        assert torch.allclose(conv_state[nport - 1 - i].cpu(), x[sl][-(taps - 1):])
+
+
 # ---- the engine on a GPU ----------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_engine_fp32_against_oracle(cuda_device, name):
