@@ -42,12 +42,15 @@ _SERVE_COMMON = ["common", "gemm", "activation", "moe", "comm/watchdog.cu"]    #
 COMPONENTS = {
     "serve": _SERVE_COMMON + ["norm", "rope", "swiglu", "serve", "attention/latent_attention.cu", "attention/latent_attention_t5.cu",
                               "attention/pooled_window_attention.cu", "attention/pooled_window_attention_mma.cu",
-                              "attention/diff_attention.cu", "recurrent"],
+                              "attention/diff_attention.cu", "attention/softcap_window_attention.cu", "recurrent"],
     # what trace replay of one design needs and no more (the library grows when another component is asked for later)
     "serve-nafazen": _SERVE_COMMON + ["norm/scalar_rmsnorm.cu", "attention/latent_attention.cu", "attention/latent_attention_t5.cu"],
     "serve-teluzen": _SERVE_COMMON + ["norm/sandwich_norm.cu", "attention/pooled_window_attention.cu",
                                       "attention/pooled_window_attention_mma.cu"],
     "serve-namisun": _SERVE_COMMON + ["norm/scalar_rmsnorm.cu", "norm/parallel_norm.cu", "attention/diff_attention.cu", "recurrent"],
+    "serve-tupidra": _SERVE_COMMON + ["norm/scalar_rmsnorm.cu", "norm/sandwich_norm.cu", "norm/canon_norm.cu",
+                                      "attention/latent_attention.cu", "attention/latent_attention_t5.cu",
+                                      "attention/softcap_window_attention.cu", "recurrent/selective_scan.cu"],
     "all": None,
 }
 

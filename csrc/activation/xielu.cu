@@ -8,6 +8,8 @@
 //   squared ReLU : max(z, 0)^2
 //   clamped gate : g' = min(gate, limit), u' = clamp(up, -limit, limit); out = g' sigmoid(alpha g') (u' + 1), packed like
 //                  the gated SiLU
+//   gated GELU   : out = gelu_tanh(gate) * up, packed like the gated SiLU
+//   sigmoid gate : y *= sigmoid(z) in place, z a strided view of pre-activation gates
 // Reference: none (the reference has no model code).
 #include "../common/dtype.cuh"
 
@@ -34,6 +36,33 @@ gated_silu_kernel(const T* __restrict__ gu, long long ld, T* __restrict__ out, i
     const int c = static_cast<int>(i % F);
     const float g = to_f32(gu[r * ld + c]), u = to_f32(gu[r * ld + F + c]);
     out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+// tanh form of GELU on the gate of a packed [gate | up] activation: 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * up
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_gelu_tanh_kernel(const T* __restrict__ gu, long long ld, T* __restrict__ out, int rows, int F) {
+  const long long n = static_cast<long long>(rows) * F;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / F;
+    const int c = static_cast<int>(i % F);
+    const float g = to_f32(gu[r * ld + c]), u = to_f32(gu[r * ld + F + c]);
+    out[i] = from_f32<T>(0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u);
+  }
+}
+
+// y[r, c] *= sigmoid(z[r, c]) in place; z is a strided view (row stride ldz) of pre-activation gates
+template <typename T>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(T* __restrict__ y, const T* __restrict__ z, long long ldz, int rows, int F) {
+  const long long n = static_cast<long long>(rows) * F;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / F;
+    const int c = static_cast<int>(i % F);
+    y[i] = from_f32<T>(to_f32(y[i]) / (1.f + expf(-to_f32(z[r * ldz + c]))));
   }
 }
 
@@ -83,6 +112,24 @@ LLMCTL_API int llmctl_gated_silu(const void* gate_up, long long ld, void* out, i
   if (rows == 0 || F == 0) return 0;
   LLMCTL_DISPATCH_DTYPE(is_fp32, T, (gated_silu_kernel<T><<<grid_for(static_cast<long long>(rows) * F), 256, 0, (cudaStream_t)stream>>>(
                                         (const T*)gate_up, ld, (T*)out, rows, F)));
+  LLMCTL_RETURN_LAST();
+}
+
+LLMCTL_API int llmctl_gated_gelu_tanh(const void* gate_up, long long ld, void* out, int is_fp32, int rows, int F, void* stream) {
+  LLMCTL_BEGIN();
+  LLMCTL_REQUIRE(ld >= 2LL * F);
+  if (rows == 0 || F == 0) return 0;
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (gated_gelu_tanh_kernel<T><<<grid_for(static_cast<long long>(rows) * F), 256, 0, (cudaStream_t)stream>>>(
+                                        (const T*)gate_up, ld, (T*)out, rows, F)));
+  LLMCTL_RETURN_LAST();
+}
+
+LLMCTL_API int llmctl_sigmoid_gate(void* y, const void* z, long long ldz, int is_fp32, int rows, int F, void* stream) {
+  LLMCTL_BEGIN();
+  LLMCTL_REQUIRE(ldz >= F);
+  if (rows == 0 || F == 0) return 0;
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (sigmoid_gate_kernel<T><<<grid_for(static_cast<long long>(rows) * F), 256, 0, (cudaStream_t)stream>>>(
+                                        (T*)y, (const T*)z, ldz, rows, F)));
   LLMCTL_RETURN_LAST();
 }
 

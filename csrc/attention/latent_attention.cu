@@ -79,7 +79,7 @@ latent_attention_kernel(const float* __restrict__ ql, long long ql_st, long long
                         const T* __restrict__ cache, const int* __restrict__ block_tables, int max_blocks,
                         int block_size, const int* __restrict__ tiles, const int* __restrict__ positions,
                         const float* __restrict__ freq, float mult, float scale, int H, int R, int dr, int heads_per_tile,
-                        int keys_per_split, T* __restrict__ out, float* __restrict__ partial) {
+                        int keys_per_split, T* __restrict__ out, float* __restrict__ partial, const float* __restrict__ sinks) {
   extern __shared__ float smem[];
   const int D = R + dr, Dp = D + 1;
   float* qs = smem;                      // [kRows][Dp]
@@ -100,8 +100,10 @@ latent_attention_kernel(const float* __restrict__ ql, long long ql_st, long long
   const int* bt = block_tables + static_cast<long long>(seq) * max_blocks;
 
   if (tid < kRows) {
-    row_m[tid] = -INFINITY;
-    row_l[tid] = 0.f;
+    // a sink is a key without a value: it is the row's initial (maximum, sum) in the first slice of the keys
+    const bool sink = sinks != nullptr && split == 0 && tid < nrows;
+    row_m[tid] = sink ? sinks[h0 + tid % nh] : -INFINITY;
+    row_l[tid] = sink ? 1.f : 0.f;
     row_c[tid] = 1.f;
     row_pos[tid] = tid < nrows ? positions[tok0 + tid / nh] : -1;
   }
@@ -256,7 +258,7 @@ static int launch_latent_attention(const float* ql, long long ql_st, long long q
                                    const int* block_tables, int max_blocks, int block_size, const int* tiles, int ntiles,
                                    const int* positions, const float* freq, float mult, float scale, int H, int R, int dr,
                                    int heads_per_tile, int splits, int keys_per_split, void* out, float* partial,
-                                   int tokens, cudaStream_t s) {
+                                   int tokens, const float* sinks, cudaStream_t s) {
   const int D = R + dr;
   const size_t smem = (static_cast<size_t>(kRows + kKeys) * (D + 1) + kRows * kKeys + 4 * kRows) * sizeof(float);
   if (smem > 227 * 1024) return static_cast<int>(cudaErrorInvalidValue);
@@ -269,7 +271,7 @@ static int launch_latent_attention(const float* ql, long long ql_st, long long q
     if (e != cudaSuccess) return static_cast<int>(e);                                                                \
     kern<<<grid, kAttnThreads, smem, s>>>(ql, ql_st, ql_sh, (const T*)q, ldq, dn, (const T*)cache, block_tables, max_blocks, \
                                           block_size, tiles, positions, freq, mult, scale, H, R, dr, heads_per_tile, \
-                                          keys_per_split, (T*)out, partial);                                         \
+                                          keys_per_split, (T*)out, partial, sinks);                                  \
   } while (0)
   if (nc <= 1) LAUNCH(1);
   else if (nc <= 2) LAUNCH(2);
@@ -300,7 +302,8 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
                            const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_tables, int max_blocks,
                            int block_size, const int* __restrict__ tiles, const int* __restrict__ positions,
                            const float* __restrict__ freq, float mult, float scale, int H, int R, int dr, int heads_per_tile,
-                           int keys_per_split, int stages, __nv_bfloat16* __restrict__ out, float* __restrict__ partial) {
+                           int keys_per_split, int stages, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
+                           const float* __restrict__ sinks) {
   constexpr int kR = 16 * MT, kWarps = 8 * MT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = R + dr, Dp = D + 8;
@@ -324,8 +327,10 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
   const int* bt = block_tables + static_cast<long long>(seq) * max_blocks;
 
   if (tid < kR) {
-    row_m[tid] = -INFINITY;
-    row_l[tid] = 0.f;
+    // a sink is a key without a value: it is the row's initial (maximum, sum) in the first slice of the keys
+    const bool sink = sinks != nullptr && split == 0 && tid < nrows;
+    row_m[tid] = sink ? sinks[h0 + tid % nh] : -INFINITY;
+    row_l[tid] = sink ? 1.f : 0.f;
     row_c[tid] = 1.f;
     row_pos[tid] = tid < nrows ? positions[tok0 + tid / nh] : -1;
   }
@@ -500,7 +505,7 @@ static int launch_latent_attention_tc(const TQ* ql, long long ql_st, long long q
                                       const int* block_tables, int max_blocks, int block_size, const int* tiles, int ntiles,
                                       const int* positions, const float* freq, float mult, float scale, int H, int R, int dr,
                                       int heads_per_tile, int splits, int keys_per_split, void* out, float* partial,
-                                      int tokens, int rows, cudaStream_t s) {
+                                      int tokens, int rows, const float* sinks, cudaStream_t s) {
   // A second key-tile stage overlaps the copy of the next tile with the products of this one.  16-row tiles take it
   // only while two CTAs still share an SM (they overlap each other's copies anyway); 32-row tiles whenever it fits
   // (up to R + dr = 576 it does).
@@ -516,7 +521,7 @@ static int launch_latent_attention_tc(const TQ* ql, long long ql_st, long long q
     if (e != cudaSuccess) return static_cast<int>(e);                                                                \
     kern<<<grid, 256 * MT, smem, s>>>(ql, ql_st, ql_sh, (const __nv_bfloat16*)q, ldq, dn, (const __nv_bfloat16*)cache, \
                                       block_tables, max_blocks, block_size, tiles, positions, freq, mult, scale,     \
-                                      H, R, dr, heads_per_tile, keys_per_split, stages, (__nv_bfloat16*)out, partial); \
+                                      H, R, dr, heads_per_tile, keys_per_split, stages, (__nv_bfloat16*)out, partial, sinks); \
   } while (0)
 #define LAUNCH_TC_NT(MT)          \
   do {                            \
@@ -551,6 +556,7 @@ LLMCTL_API int llmctl_latent_kv_write(const void* d, long long ld, int Q, int R,
 }
 
 // partial: fp32 scratch of tokens * H * splits * (R + 2) numbers when splits > 1 (may be null otherwise).
+// sinks: fp32 [H] or null; exp(sinks[h]) (not scaled) joins the softmax denominator of head h.
 // ql: absorbed queries, element (token, head, c) at ql[token * ql_st + head * ql_sh + c]; fp32, or bf16 (ql_bf16) on the
 // tensor-core path only (llmctl_latent_attention_uses_tensor_cores).
 LLMCTL_API int llmctl_latent_attention_uses_tensor_cores(int is_fp32, int R, int dr, int rows_per_tile) {
@@ -562,7 +568,7 @@ LLMCTL_API int llmctl_latent_attention(const void* ql, int ql_bf16, long long ql
                                        int ntiles, int tokens, const int* positions, const float* freq, float mult,
                                        float scale, int H, int R, int dr, int heads_per_tile, int splits,
                                        int keys_per_split, void* out, float* partial, int is_fp32, int tensor_cores,
-                                       int rows_per_tile, void* stream) {
+                                       int rows_per_tile, const float* sinks, void* stream) {
   LLMCTL_BEGIN();
   LLMCTL_REQUIRE(H > 0 && R > 0 && dr >= 0 && dr % 2 == 0 && block_size > 0 && heads_per_tile >= 1 &&
                  heads_per_tile <= rows_per_tile && (rows_per_tile == 16 || rows_per_tile == 32) && splits >= 1 && keys_per_split > 0 && (splits == 1 || partial != nullptr));
@@ -572,11 +578,11 @@ LLMCTL_API int llmctl_latent_attention(const void* ql, int ql_bf16, long long ql
     if (ql_bf16)
       rc = launch_latent_attention_tc<__nv_bfloat16>((const __nv_bfloat16*)ql, ql_st, ql_sh, q, ldq, dn, cache, block_tables, max_blocks,
                                                      block_size, tiles, ntiles, positions, freq, mult, scale, H, R, dr, heads_per_tile,
-                                                     splits, keys_per_split, out, partial, tokens, rows_per_tile, (cudaStream_t)stream);
+                                                     splits, keys_per_split, out, partial, tokens, rows_per_tile, sinks, (cudaStream_t)stream);
     else
     rc = launch_latent_attention_tc<float>((const float*)ql, ql_st, ql_sh, q, ldq, dn, cache, block_tables, max_blocks, block_size, tiles, ntiles, positions, freq,
                                     mult, scale, H, R, dr, heads_per_tile, splits, keys_per_split, out, partial, tokens,
-                                    rows_per_tile, (cudaStream_t)stream);
+                                    rows_per_tile, sinks, (cudaStream_t)stream);
     if (rc != 0) LLMCTL_FAIL(rc, "latent attention launch");
     LLMCTL_RETURN_LAST();
   }
@@ -584,7 +590,7 @@ LLMCTL_API int llmctl_latent_attention(const void* ql, int ql_bf16, long long ql
   LLMCTL_DISPATCH_DTYPE(is_fp32, T, (rc = launch_latent_attention<T>((const float*)ql, ql_st, ql_sh, q, ldq, dn, cache, block_tables, max_blocks, block_size,
                                                                      tiles, ntiles, positions, freq, mult, scale, H, R, dr,
                                                                      heads_per_tile, splits, keys_per_split, out, partial,
-                                                                     tokens, (cudaStream_t)stream)));
+                                                                     tokens, sinks, (cudaStream_t)stream)));
   if (rc != 0) LLMCTL_FAIL(rc, "latent attention launch");
   LLMCTL_RETURN_LAST();
 }

@@ -82,7 +82,7 @@ latent_attention_t5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
                            const int* __restrict__ block_tables, int max_blocks, int block_size,
                            const int* __restrict__ tiles, const int* __restrict__ positions, float scale, int H, int R,
                            int dr, int heads_per_tile, int keys_per_split, int nsplit, int q_rows_are_heads,
-                           __nv_bfloat16* __restrict__ out, float* __restrict__ partial) {
+                           __nv_bfloat16* __restrict__ out, float* __restrict__ partial, const float* __restrict__ sinks) {
   using namespace t5;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_q, bar_kfull[2], bar_kempty[2], bar_s[2], bar_p, bar_pv;
@@ -251,7 +251,9 @@ latent_attention_t5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     const int pos = valid ? positions[tok] : -1;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
     const float scale_log2 = scale * kLog2e;
-    float m_ref = -INFINITY, l = 0.f;
+    // a sink (a key without a value) is the row's initial (reference, sum) in the first slice of the keys
+    const bool sink = sinks != nullptr && split == 0 && valid;
+    float m_ref = sink ? sinks[h] * kLog2e : -INFINITY, l = sink ? 1.f : 0.f;
     bool ok = true;
     for (int i = 0; i < ntile; ++i) {
       const int st = i & 1;
@@ -388,7 +390,7 @@ LLMCTL_API int llmctl_latent_attention_t5(const void* ql, int ql_bf16, long long
                                           const int* block_tables, int max_blocks, int block_size, const int* tiles,
                                           int ntiles, int tokens, const int* positions, const float* freq, float mult,
                                           float scale, int H, int R, int dr, int heads_per_tile, int splits,
-                                          int keys_per_split, void* qfull, void* out, float* partial, void* stream) {
+                                          int keys_per_split, void* qfull, void* out, float* partial, const float* sinks, void* stream) {
   LLMCTL_BEGIN();
   LLMCTL_REQUIRE(llmctl_latent_attention_t5_ok(R, dr, block_size) && H > 0 && heads_per_tile >= 1 &&
                  heads_per_tile <= t5::kRows && splits >= 1 && keys_per_split > 0 && keys_per_split % t5::kKeys == 0 &&
@@ -415,7 +417,7 @@ LLMCTL_API int llmctl_latent_attention_t5(const void* ql, int ql_bf16, long long
   dim3 grid(ntiles, (H + heads_per_tile - 1) / heads_per_tile, splits * ncg);
   latent_attention_t5_kernel<<<grid, t5::kThreads, smem, s>>>(tmQ, tmK, block_tables, max_blocks, block_size, tiles, positions,
                                                                scale, H, R, dr, heads_per_tile, keys_per_split, splits,
-                                                               rows_are_heads, (__nv_bfloat16*)out, splits > 1 ? partial : nullptr);
+                                                               rows_are_heads, (__nv_bfloat16*)out, splits > 1 ? partial : nullptr, sinks);
   if (splits > 1) {
     rc = launch_latent_attention_merge_bf16(partial, out, R, splits, tokens * H, s);
     if (rc) LLMCTL_FAIL(rc, "merge");

@@ -1,4 +1,5 @@
-"""Feed-forward layers for inference batches: two-matrix MLPs with the xIELU or the squared-ReLU activation and a
+"""Feed-forward layers for inference batches: two-matrix MLPs with the xIELU or the squared-ReLU activation, a gated
+MLP with the tanh form of GELU on the gate, and a
 routed mixture of gated experts (sigmoid, softmax or chosen-logit softmax weights) with an optional shared expert.
 
 Reference: none — the reference has no model code (reference llmctl/runtime/engine.py:119-140)."""
@@ -52,6 +53,23 @@ class SquaredReluMLP(nn.Module):
 
     def forward(self, h: torch.Tensor, x32: torch.Tensor) -> torch.Tensor:
         return ops.linear(eops.relu_squared(ops.linear(h, self.up)), self.down)
+
+
+class GatedGeluMLP(nn.Module):
+    """``Wdown (gelu_tanh(Wgate h) * (Wup h))``; gate and up run as one packed GEMM."""
+
+    def __init__(self, width: int, ff: int, dtype, device):
+        super().__init__()
+        self.gate_up = nn.Parameter(torch.empty(2 * ff, width, dtype=dtype, device=device))       # [gate ; up]
+        self.down = nn.Parameter(torch.empty(width, ff, dtype=dtype, device=device))
+
+    def load(self, get, prefix: str) -> None:
+        with torch.no_grad():
+            self.gate_up.copy_(torch.cat([get(prefix + "gate"), get(prefix + "up")], dim=0))
+            self.down.copy_(get(prefix + "down"))
+
+    def forward(self, h: torch.Tensor, x32: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return ops.linear(eops.gated_gelu_tanh(ops.linear(h, self.gate_up)), self.down)
 
 
 class GatedExpertMoE(nn.Module):

@@ -12,6 +12,20 @@ single rotated key part shared by all heads.  Queries go through their own norme
     ol       = attention over the cache rows (ops.latent_attention.latent_attention)   [T, H, R]
     out      = (ol Uv_h^T) Wo^T
 
+Optional parts of ``LatentAttention`` (fields of its spec): ``sink`` — a learned number per head whose exponential joins
+the softmax denominator (a key without a value, not scaled); ``out_gate`` — the concatenated heads are multiplied element
+by element with the sigmoid of one more projection of the mixer's input (packed into the down-projection GEMM).
+
+``SoftcapWindowAttention``: grouped-query attention without rotation whose scores pass a tanh soft cap and lose a linear
+distance bias with one slope per head; a sliding window that also keeps the first tokens of the sequence; a softmax with
+one added to the denominator (a sink of score 0); values cached at unit RMS per head; projection biases; a sigmoid output
+gate.  Every part is a field of ``SoftcapWindowAttentionSpec``.  Per step:
+
+    p        = h Wp^T                           (one packed GEMM: q | k | v | gate)
+    q, cache = bias / value norm / append       (ops.softcap_attention.window_kv_append)
+    o        = attention over kept + window keys, gate      (ops.softcap_attention.softcap_window_attention)
+    out      = o Wo^T + bo
+
 ``PooledWindowAttention``: grouped-query attention over a sliding window of ``window`` tokens plus one pooled key/value
 (the mean of the cached keys / values) per block of ``pool`` tokens that lies wholly before the window.  Optional parts,
 each a field of ``PooledWindowAttentionSpec``: projection biases, an RMS norm over the whole q and the whole k
@@ -61,8 +75,9 @@ from ..ops import diff_attention as dops
 from ..ops import functional as ops
 from ..ops import latent_attention as lops
 from ..ops import recurrent as rops
+from ..ops import softcap_attention as sops
 from ..ops import window_attention as wops
-from ..ops.elementwise import rope_frequencies
+from ..ops.elementwise import rope_frequencies, sigmoid_gate_
 
 
 @dataclass
@@ -77,6 +92,8 @@ class LatentAttentionSpec:
     rot_base: float
     rot_scaling: Optional[Dict[str, Any]] = None
     kv_from: Optional[int] = None       # index of the layer whose cache this layer reads
+    sink: bool = False                  # a learned number per head joins the softmax denominator
+    out_gate: bool = False              # heads * sigmoid(Wg h) before the output projection
 
     @property
     def cache_width(self) -> int:
@@ -84,14 +101,18 @@ class LatentAttentionSpec:
 
 
 class LatentAttention(nn.Module):
+    stateful = False
+
     def __init__(self, width: int, spec: LatentAttentionSpec, eps: float, dtype, device):
         super().__init__()
         s = self.spec = spec
         self.eps = eps
         own = s.kv_from is None
         kw = dict(dtype=dtype, device=device)
-        rows = s.q_rank + (s.kv_rank + s.rot_dim if own else 0)
-        self.w_down = nn.Parameter(torch.empty(rows, width, **kw))                      # [dq ; dkv]
+        self.n_down = s.q_rank + (s.kv_rank + s.rot_dim if own else 0)
+        rows = self.n_down + (s.heads * s.vdim if s.out_gate else 0)
+        self.w_down = nn.Parameter(torch.empty(rows, width, **kw))                      # [dq ; dkv ; gate]
+        self.sink = nn.Parameter(torch.zeros(s.heads, dtype=torch.float32, device=device)) if s.sink else None
         self.q_norm = nn.Parameter(torch.ones(s.q_rank, **kw))
         self.kv_norm = nn.Parameter(torch.ones(s.kv_rank, **kw)) if own else None
         self.w_uq = nn.Parameter(torch.empty(s.heads * (s.dim + s.rot_dim), s.q_rank, **kw))
@@ -104,8 +125,10 @@ class LatentAttention(nn.Module):
     def load(self, get, prefix: str) -> None:
         s = self.spec
         with torch.no_grad():
-            parts = [get(prefix + "dq")] + ([get(prefix + "dkv")] if s.kv_from is None else [])
+            parts = [get(prefix + "dq")] + ([get(prefix + "dkv")] if s.kv_from is None else []) + ([get(prefix + "g")] if s.out_gate else [])
             self.w_down.copy_(torch.cat(parts, dim=0))
+            if s.sink:
+                self.sink.copy_(get(prefix + "sink").float())
             self.q_norm.copy_(get(prefix + "dq.norm"))
             if s.kv_from is None:
                 self.kv_norm.copy_(get(prefix + "dkv.norm"))
@@ -142,9 +165,14 @@ class LatentAttention(nn.Module):
             rows = lops.rows_per_tile(q.dtype, s.kv_rank, s.rot_dim, q.is_cuda, s.heads if batch.decode_only else lops.ROWS_PER_TILE_WIDE)
         ol = lops.latent_attention(ql, q, s.dim, cache, batch.block_tables, batch.tiles(rows), batch.positions,
                                    self.rot_freq, self.rot_mult, s.scale, batch.heads_per_tile(s.heads, rows), batch.max_context,
-                                   batch.attention_splits(s.heads, rows), rows=rows)
+                                   batch.attention_splits(s.heads, rows), rows=rows, sinks=self.sink)
         o = torch.bmm(ol.transpose(0, 1), self.w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, s.heads * s.vdim)
+        if s.out_gate:
+            o = sigmoid_gate_(o, d[:, self.n_down:])
         return ops.linear(o, self.w_o)
+
+    def cache_shape(self, num_blocks: int, block_size: int) -> Tuple[int, ...]:
+        return (num_blocks, block_size, self.spec.cache_width)
 
 
 @dataclass
@@ -240,6 +268,76 @@ class PooledWindowAttention(nn.Module):
                                          s.scale, s.heads, s.kv_heads, s.dim, s.vdim, s.window, pool, bs, h.dtype,
                                          max_context=batch.max_context)
         return ops.linear(o, self.w_o), v_first
+
+
+@dataclass
+class SoftcapWindowAttentionSpec:
+    heads: int
+    kv_heads: int
+    dim: int            # query/key size per head
+    vdim: int           # value size per head
+    scale: float
+    softcap: float = 0.0        # scores become softcap * tanh(score / softcap); 0: no cap
+    window: int = 0             # position i sees j <= i with i - j < window; 0: every earlier token
+    keep_first: int = 0         # ... or j < keep_first
+    distance_bias: bool = True  # slope_h (i - j) is taken off the score, slope_h = 2^(-8 (h + 1) / heads)
+    sink_one: bool = True       # one is added to the softmax denominator (a sink of score 0 without a value)
+    value_norm: bool = True     # every value head is cached at unit RMS (no weight)
+    bias: bool = True           # q, k, v and output projections have biases
+    out_gate: bool = True       # heads * sigmoid(Wg h) before the output projection
+
+    @property
+    def cache_width(self) -> int:
+        return self.kv_heads * (self.dim + self.vdim)
+
+
+class SoftcapWindowAttention(nn.Module):
+    stateful = False
+
+    def __init__(self, width: int, spec: SoftcapWindowAttentionSpec, eps: float, dtype, device):
+        super().__init__()
+        s = self.spec = spec
+        if s.heads % s.kv_heads or s.window < 0 or s.keep_first < 0 or s.softcap < 0:
+            raise ValueError(f"inconsistent attention sizes: {s}")
+        self.eps = eps
+        kw = dict(dtype=dtype, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        self.nq, self.nk, self.nv = s.heads * s.dim, s.kv_heads * s.dim, s.kv_heads * s.vdim
+        self.n_qkv = self.nq + self.nk + self.nv
+        self.w_in = nn.Parameter(torch.empty(self.n_qkv + (s.heads * s.vdim if s.out_gate else 0), width, **kw))     # [q ; k ; v ; gate]
+        self.b_in = nn.Parameter(torch.zeros(self.n_qkv, **f32)) if s.bias else None
+        self.w_o = nn.Parameter(torch.empty(width, s.heads * s.vdim, **kw))
+        self.b_o = nn.Parameter(torch.zeros(width, **f32)) if s.bias else None
+        self.register_buffer("slopes", sops.distance_slopes(s.heads).to(device) if s.distance_bias else None, persistent=False)
+        self.register_buffer("sinks", torch.zeros(s.heads, **f32) if s.sink_one else None, persistent=False)
+
+    def load(self, get, prefix: str) -> None:
+        """Checkpoint names under ``prefix``: q, k, v (+ ``.b`` biases), g, o (+ ``o.b``)."""
+        s = self.spec
+        with torch.no_grad():
+            parts = [get(prefix + "q"), get(prefix + "k"), get(prefix + "v")] + ([get(prefix + "g")] if s.out_gate else [])
+            self.w_in.copy_(torch.cat(parts, dim=0))
+            self.w_o.copy_(get(prefix + "o"))
+            if s.bias:
+                self.b_in.copy_(torch.cat([get(prefix + "q.b"), get(prefix + "k.b"), get(prefix + "v.b")], dim=0).float())
+                self.b_o.copy_(get(prefix + "o.b").float())
+
+    def cache_shape(self, num_blocks: int, block_size: int) -> Tuple[int, ...]:
+        return (num_blocks, block_size, self.spec.cache_width)
+
+    def forward(self, h: torch.Tensor, batch, cache: torch.Tensor) -> torch.Tensor:
+        """h: [T, W] in the activation type; ``cache``: this layer's [pages, bs, G (d + e)]."""
+        s = self.spec
+        p = ops.linear(h, self.w_in)
+        q = sops.window_kv_append(p, self.b_in, s.heads, s.kv_heads, s.dim, s.vdim, s.value_norm, self.eps, batch.slots, cache)
+        gate = p[:, self.n_qkv:] if s.out_gate else None
+        # prompt portions: tiles of 128 tokens on the tensor-core kernel, of 16 on the FMA kernel; decoded tokens: one each
+        width = sops.tile_width(cache.dtype, s.heads, s.kv_heads, s.dim, s.vdim, q.is_cuda, batch.decode_only)
+        o = sops.softcap_window_attention(q, cache, batch.block_tables, batch.tiles(width), 1 if batch.decode_only else width,
+                                          batch.positions, gate, self.slopes, self.sinks, s.scale, s.softcap, s.window, s.keep_first,
+                                          s.heads, s.kv_heads, s.dim, s.vdim, batch.block_size, h.dtype, max_context=batch.max_context)
+        y = ops.linear(o, self.w_o)
+        return y if self.b_o is None else torch.add(y, self.b_o)        # fp32 sum: the residual update takes either type
 
 
 @dataclass

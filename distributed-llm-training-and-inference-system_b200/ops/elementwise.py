@@ -27,6 +27,8 @@ native.register_signature("llmctl_embed_scale", [c_void_p, c_void_p, c_int, c_fl
 native.register_signature("llmctl_softcap", [c_void_p, c_ll, c_float, c_void_p])
 native.register_signature("llmctl_xielu", [c_void_p, c_void_p, c_int, c_ll, c_float, c_float, c_void_p])
 native.register_signature("llmctl_gated_silu", [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_void_p])
+native.register_signature("llmctl_gated_gelu_tanh", [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_void_p])
+native.register_signature("llmctl_sigmoid_gate", [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p])
 native.register_signature("llmctl_relu_squared", [c_void_p, c_void_p, c_int, c_ll, c_void_p])
 native.register_signature("llmctl_embed_positions", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
 native.register_signature("llmctl_rmsnorm_rows", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
@@ -157,6 +159,31 @@ def gated_silu(gate_up: torch.Tensor) -> torch.Tensor:
         return out
     g, u = gate_up.float().chunk(2, dim=-1)
     return (F.silu(g) * u).to(gate_up.dtype)
+
+
+def gated_gelu_tanh(gate_up: torch.Tensor) -> torch.Tensor:
+    """``gelu_tanh(gate) * up`` of a packed [rows, 2F] activation (gate first), bf16 or fp32;
+    ``gelu_tanh(g) = g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))``."""
+    rows, F2 = gate_up.shape
+    if gate_up.is_cuda:
+        assert gate_up.stride(1) == 1
+        out = torch.empty(rows, F2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+        native.call("llmctl_gated_gelu_tanh", gate_up.data_ptr(), gate_up.stride(0), out.data_ptr(), _is32(gate_up), rows, F2 // 2,
+                    native.stream_ptr())
+        return out
+    g, u = gate_up.float().chunk(2, dim=-1)
+    return (F.gelu(g, approximate="tanh") * u).to(gate_up.dtype)
+
+
+def sigmoid_gate_(y: torch.Tensor, z: torch.Tensor) -> torch.Tensor:
+    """``y *= sigmoid(z)`` in place; y: contiguous [rows, F]; z: [rows, F] pre-activation gates, a view with unit column
+    stride of the same type."""
+    rows, Fc = y.shape
+    assert y.is_contiguous() and z.shape == y.shape and z.stride(1) == 1 and z.dtype == y.dtype
+    if y.is_cuda:
+        native.call("llmctl_sigmoid_gate", y.data_ptr(), z.data_ptr(), z.stride(0), _is32(y), rows, Fc, native.stream_ptr())
+        return y
+    return y.copy_((y.float() * torch.sigmoid(z.float())).to(y.dtype))
 
 
 def relu_squared(z: torch.Tensor) -> torch.Tensor:

@@ -20,13 +20,13 @@ native.register_signature("llmctl_latent_kv_write", [c_void_p, c_ll, c_int, c_in
                                                       c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p])
 native.register_signature("llmctl_latent_attention", [c_void_p, c_int, c_ll, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                                        c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int,
-                                                       c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+                                                       c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
 native._KERNELS_PER_CALL["llmctl_latent_attention"] = 1
 native.register_signature("llmctl_latent_attention_t5_ok", [c_int, c_int, c_int])
 native.register_signature("llmctl_latent_attention_t5_status", [c_int])
 native.register_signature("llmctl_latent_attention_t5", [c_void_p, c_int, c_ll, c_ll, c_void_p, c_ll, c_int, c_void_p, c_ll, c_void_p, c_int, c_int,
                                                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int,
-                                                          c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+                                                          c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
 native._KERNELS_PER_CALL["llmctl_latent_attention_t5"] = 2
 
 ROWS_PER_TILE = 16          # query rows (token, head) a CTA owns; tiles are built by the engine with this limit
@@ -93,11 +93,12 @@ def latent_kv_write(d: torch.Tensor, Q: int, R: int, dr: int, wq: torch.Tensor, 
 def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Tensor, block_tables: torch.Tensor,
                      tiles: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, mult: float, scale: float,
                      heads_per_tile: int, max_context: int, splits: int = 1, tensor_cores: bool = True,
-                     rows: int = ROWS_PER_TILE) -> torch.Tensor:
+                     rows: int = ROWS_PER_TILE, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """ql: [T, H, R] absorbed queries (any token / head strides; fp32, or bf16 where ``uses_tensor_cores``); q: [T, H * (dn + dr)] raw queries (the rope part of each head is rotated
     here); tiles: int32 [n, 4] = (first token row, tokens, block-table row, 0) with tokens * heads_per_tile <=
     ``rows`` (16, or 32 where ``rows_per_tile`` says so), all tokens of a tile in one sequence with growing positions.  Returns [T, H, R] in q's type:
-    softmax(scale * (ql . c + rot(qr) . kr)) c over cache positions 0..position of each token."""
+    softmax(scale * (ql . c + rot(qr) . kr)) c over cache positions 0..position of each token.  ``sinks``: fp32 [H] or None;
+    ``exp(sinks[h])`` (not scaled) joins the softmax denominator of head h: a key without a value."""
     T, H, R = ql.shape
     D = cache.shape[-1]
     dr = D - R
@@ -116,13 +117,13 @@ def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Te
                         q.data_ptr(), q.stride(0), dn, cache.data_ptr(), cache.shape[0] * block_size, block_tables.data_ptr(),
                         block_tables.shape[1], block_size, tiles.data_ptr(), tiles.shape[0], T, positions.data_ptr(),
                         freq.data_ptr(), float(mult), float(scale), H, R, dr, heads_per_tile, splits, per, qfull.data_ptr(),
-                        out.data_ptr(), native.ptr(partial), native.stream_ptr())
+                        out.data_ptr(), native.ptr(partial), native.ptr(sinks), native.stream_ptr())
             return out
         native.call("llmctl_latent_attention", ql.data_ptr(), int(ql.dtype == torch.bfloat16), ql.stride(0), ql.stride(1),
                     q.data_ptr(), q.stride(0), dn, cache.data_ptr(),
                     block_tables.data_ptr(), block_tables.shape[1], block_size, tiles.data_ptr(), tiles.shape[0], T,
                     positions.data_ptr(), freq.data_ptr(), float(mult), float(scale), H, R, dr, heads_per_tile, splits, per,
-                    out.data_ptr(), native.ptr(partial), _is32(q), int(tensor_cores), int(rows), native.stream_ptr())
+                    out.data_ptr(), native.ptr(partial), _is32(q), int(tensor_cores), int(rows), native.ptr(sinks), native.stream_ptr())
         return out
     out = torch.zeros(T, H, R, dtype=torch.float32)
     rows = cache.view(-1, D).float()
@@ -135,5 +136,9 @@ def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Te
             kv = rows[bt[j // block_size] * block_size + j % block_size]          # [p + 1, D]
             qr = rotate_interleaved(qh[t, :, dn:], positions[t:t + 1].expand(H), freq, mult)
             s = (ql[t].float() @ kv[:, :R].t() + qr @ kv[:, R:].t()) * scale
-            out[t] = torch.softmax(s, -1) @ kv[:, :R]
+            if sinks is not None:
+                s = torch.cat([s, sinks.float()[:, None]], dim=-1)
+                out[t] = torch.softmax(s, -1)[:, :-1] @ kv[:, :R]
+            else:
+                out[t] = torch.softmax(s, -1) @ kv[:, :R]
     return out.to(q.dtype)

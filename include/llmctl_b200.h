@@ -234,7 +234,8 @@ int llmctl_latent_attention(const void* ql, int ql_bf16, long long ql_st, long l
                             int dn, const void* cache, const int* block_tables, int max_blocks, int block_size,
                             const int* tiles, int ntiles, int tokens, const int* positions, const float* freq, float mult,
                             float scale, int H, int R, int dr, int heads_per_tile, int splits, int keys_per_split,
-                            void* out, float* partial, int is_fp32, int tensor_cores, int rows_per_tile, void* stream);
+                            void* out, float* partial, int is_fp32, int tensor_cores, int rows_per_tile,
+                            const float* sinks /* fp32 [H] or null: exp(sinks[h]) joins head h's softmax denominator */, void* stream);
 /* The tcgen05 kernel (128-row query tiles): sizes that qualify, status of its bounded waits, and the launch.
  * qfull: bf16 scratch [tokens, H, R + dr]; cache_rows = blocks x block_size. */
 int llmctl_latent_attention_t5_ok(int R, int dr, int block_size);
@@ -243,7 +244,7 @@ int llmctl_latent_attention_t5(const void* ql, int ql_bf16, long long ql_st, lon
                                int dn, const void* cache, long long cache_rows, const int* block_tables, int max_blocks,
                                int block_size, const int* tiles, int ntiles, int tokens, const int* positions,
                                const float* freq, float mult, float scale, int H, int R, int dr, int heads_per_tile,
-                               int splits, int keys_per_split, void* qfull, void* out, float* partial, void* stream);
+                               int splits, int keys_per_split, void* qfull, void* out, float* partial, const float* sinks, void* stream);
 int llmctl_moe_tile_rows(void);
 /* correction: fp32 [E] added to the scores for the CHOICE only, or null; n_groups > 1: only experts of the keep_groups
  * best groups (of E / n_groups neighbours each) can be chosen.  Ids >= the E given to plan / permute are identity
@@ -337,6 +338,31 @@ int llmctl_selective_scan(const void* u, const void* bc, long long ldbc, int off
                           const float* dt_bias, const float* A, const float* D, const void* z, long long ldz, const void* x,
                           long long ldx, const int* portions, int nportions, float* state, float* conv_state, void* out, int C,
                           int N, int taps, int is_fp32, void* stream);
+
+/* ---- pre-norm with an input convolution, soft-capped window attention (csrc/norm/canon_norm.cu,
+ *      csrc/attention/softcap_window_attention.cu, csrc/activation/xielu.cu) ---- */
+/* x += a + f in place (each optional, bf16 or fp32); r[row] = 1 / sqrt(mean(x[row]^2) + eps). */
+int llmctl_residual_rms(const void* a, int a_is_fp32, long long lda, const void* f, int f_is_fp32, long long ldf, float* x,
+                        float* r, int tokens, int W, float eps, void* stream);
+/* out_s = h_s + causal depthwise conv(h_s) over time, h_s = norm_w_s * x * r, for S = 1 or 2 sublayers; state: fp32
+ * [slots, taps - 1, W], the last unweighted normed rows of every sequence (read, then rewritten by a second launch). */
+int llmctl_norm_canon(const float* x, const float* r, int S, const float* norm_w0, const float* conv_w0, void* out0,
+                      const float* norm_w1, const float* conv_w1, void* out1, const int* portions, int nportions,
+                      const int* seq_rows, float* state, int tokens, int W, int taps, int out_is_fp32, void* stream);
+int llmctl_gated_gelu_tanh(const void* gate_up, long long ld, void* out, int is_fp32, int rows, int F, void* stream);
+int llmctl_sigmoid_gate(void* y, const void* z, long long ldz, int is_fp32, int rows, int F, void* stream);
+/* fp32 biases (or null), optional unit-RMS norm of every value head; q -> fp32, [k | v] -> cache row. */
+int llmctl_window_kv_append(const void* proj, long long ld, const float* bias, int H, int G, int d, int e, int value_norm,
+                            float eps, const long long* slots, float* q_out, void* cache, int tokens, int is_fp32, void* stream);
+int llmctl_softcap_attention_heads_per_cta(int H, int G, int tile_tokens, int use_mma);
+int llmctl_softcap_attention_mma_ok(int H, int G, int d, int e, int tile_tokens);
+/* Sliding window (0: none) with kept first tokens, tanh soft cap (0: none), per-head distance slopes and sinks (null:
+ * none), sigmoid output gate (null: none). */
+int llmctl_softcap_window_attention(const float* q, const void* cache, const int* block_tables, int max_blocks, const int* tiles,
+                                    int ntiles, int tile_tokens, const int* positions, const void* gate, long long gate_ld,
+                                    const float* slopes, const float* sinks, float scale, float cap, int window, int keep_first,
+                                    int H, int G, int d, int e, int bs, void* out, int splits, float* part_ml, float* part_o,
+                                    int is_fp32, int use_mma, void* stream);
 
 #ifdef __cplusplus
 }
