@@ -370,7 +370,9 @@ class InferenceEngine:
         if g is None:
             if len(self._graphs) > 64:
                 self._graphs.clear()
-            batch = RaggedBatch(portions, self.block_size, self.device, pad_to=(Bb, max_blocks, max_blocks * self.block_size))
+            # warm-up and capture run on padding rows only (no cache slot, no state slot): a recurrent state must see
+            # every token exactly once, and the warm-up passes would apply this step's tokens again
+            batch = RaggedBatch([], self.block_size, self.device, pad_to=(Bb, max_blocks, max_blocks * self.block_size))
             side = torch.cuda.Stream(device=self.device)
             side.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(side):
@@ -382,8 +384,7 @@ class InferenceEngine:
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 logits = self.model.forward_ragged(batch, self.caches)
             g = self._graphs[key] = (batch, graph, logits)
-        else:
-            g[0].refill(portions)
+        g[0].refill(portions)
         self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + g[0].nbytes
         g[1].replay()
         return g[2][:B]

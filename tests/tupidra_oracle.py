@@ -77,6 +77,21 @@ def latent_kv(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict[str, Any], ep
     return c, kr
 
 
+def latent_core(q: torch.Tensor, k: torch.Tensor, kr: torch.Tensor, v: torch.Tensor, sink: torch.Tensor, scale: float,
+                freqs: List[float], amp: float) -> torch.Tensor:
+    """q: [T, H, dn + dr] (rotated part last, not yet rotated); k: [T, H, dn]; kr: [T, dr] rotated; v: [T, H, dv]."""
+    T, H, dn = k.shape
+    out = torch.zeros(T, H, v.shape[2], dtype=F64)
+    for t in range(T):
+        for hd in range(H):
+            qr = rotate_pairs(q[t, hd, dn:], t, freqs, amp)
+            s = (k[:t + 1, hd] @ q[t, hd, :dn] + kr[:t + 1] @ qr) * scale
+            mx = max(float(s.max()), float(sink[hd]))
+            e = torch.exp(s - mx)
+            out[t, hd] = (e[:, None] * v[:t + 1, hd]).sum(0) / (e.sum() + math.exp(float(sink[hd]) - mx))
+    return out
+
+
 def latent_attention(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict[str, Any], eps: float, c: torch.Tensor, kr: torch.Tensor):
     T = h.shape[0]
     H, dn, dr, dv = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
@@ -86,26 +101,14 @@ def latent_attention(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict[str, A
     k = (c @ P["uk"].T).view(T, H, dn)
     v = (c @ P["uv"].T).view(T, H, dv)
     gate = torch.sigmoid(h @ P["g"].T).view(T, H, dv)
-    out = torch.zeros(T, H, dv, dtype=F64)
-    for t in range(T):
-        for hd in range(H):
-            qr = rotate_pairs(q[t, hd, dn:], t, freqs, amp)
-            s = (k[:t + 1, hd] @ q[t, hd, :dn] + kr[:t + 1] @ qr) * m["scale"]
-            mx = max(float(s.max()), float(P["sink"][hd]))
-            e = torch.exp(s - mx)
-            out[t, hd] = (e[:, None] * v[:t + 1, hd]).sum(0) / (e.sum() + math.exp(float(P["sink"][hd]) - mx))
+    out = latent_core(q, k, kr, v, P["sink"], m["scale"], freqs, amp)
     return (out * gate).reshape(T, H * dv) @ P["o"].T
 
 
-def window_attention(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict[str, Any], eps: float):
-    T = h.shape[0]
-    H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    size, keep = m["mask"]["size"], m["mask"]["keep_first"]
-    cap = m["softcap"]
-    q = (h @ P["q"].T + P["q.b"]).view(T, H, d)
-    k = (h @ P["k"].T + P["k.b"]).view(T, G, d)
-    v = rms((h @ P["v"].T + P["v.b"]).view(T, G, e), eps)
-    gate = torch.sigmoid(h @ P["g"].T).view(T, H, e)
+def window_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, cap: float, size: int, keep: int) -> torch.Tensor:
+    """q: [T, H, d]; k: [T, G, d]; v: [T, G, e] (already at unit RMS).  Returns [T, H, e]."""
+    T, H = q.shape[0], q.shape[1]
+    G, e = k.shape[1], v.shape[2]
     out = torch.zeros(T, H, e, dtype=F64)
     for i in range(T):
         for hd in range(H):
@@ -114,12 +117,23 @@ def window_attention(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict[str, A
             den, acc = 1.0, torch.zeros(e, dtype=F64)
             for j in range(i + 1):
                 if i - j < size or j < keep:
-                    s = float(q[i, hd] @ k[j, g]) * m["scale"]
+                    s = float(q[i, hd] @ k[j, g]) * scale
                     s = cap * math.tanh(s / cap) - slope * (i - j)
                     w = math.exp(s)
                     den += w
                     acc += w * v[j, g]
             out[i, hd] = acc / den
+    return out
+
+
+def window_attention(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict[str, Any], eps: float):
+    T = h.shape[0]
+    H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    q = (h @ P["q"].T + P["q.b"]).view(T, H, d)
+    k = (h @ P["k"].T + P["k.b"]).view(T, G, d)
+    v = rms((h @ P["v"].T + P["v.b"]).view(T, G, e), eps)
+    gate = torch.sigmoid(h @ P["g"].T).view(T, H, e)
+    out = window_core(q, k, v, m["scale"], m["softcap"], m["mask"]["size"], m["mask"]["keep_first"])
     return (out * gate).reshape(T, H * e) @ P["o"].T + P["o.b"]
 
 
@@ -182,13 +196,9 @@ def forward(cfg: Dict[str, Any], tensors: Dict[str, torch.Tensor], tokens: List[
             h2 = canon(n * tensors[f"l{i}.norm2"].to(F64), tensors[f"l{i}.canon2"].to(F64))
             a = a + feed_forward(h2, sub(tensors, f"l{i}.mlp."))
         x = x + a
-        if layer_out_wanted(layers_out):
+        if layers_out is not None:
             layers_out.append(x.clone())
     return (rms(x, eps) * tensors["final.norm"].to(F64)) @ tensors["head"].to(F64).T
-
-
-def layer_out_wanted(layers_out) -> bool:
-    return layers_out is not None
 
 
 def random_weights(cfg: Dict[str, Any], seed: int = 0) -> Dict[str, torch.Tensor]:
