@@ -55,7 +55,7 @@ def parse_args():
     ap.add_argument("--extras-selftest", action="store_true", help="2 GPUs: run scaled-down extra arms (plumbing check)")
     ap.add_argument("--extra-steps", type=int, default=20)
     ap.add_argument("--extras-budget-s", type=float, default=420.0)
-    ap.add_argument("--arch-compare", default=None, choices=["nafazen", "teluzen", "namisun"],
+    ap.add_argument("--arch-compare", default=None, choices=["nafazen", "teluzen", "namisun", "tupidra"],
                     help="1 GPU: serving throughput (prefill, decode) of this design beside a GPT of equal size, and its own "
                          "kernels against the roofline; the default training workload is not run")
     ap.add_argument("--arch-sizes", nargs="*", default=None, help="with --arch-compare: which built-in sizes (default all)")

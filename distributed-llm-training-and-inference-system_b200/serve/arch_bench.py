@@ -1,8 +1,9 @@
-"""Serving throughput of a ragged-batch design (Nafazen, Teluzen, Namisun) beside the GPT/LLaMA family at equal parameter count:
+"""Serving throughput of a ragged-batch design (Nafazen, Teluzen, Namisun, Tupidra) beside the GPT/LLaMA family at equal parameter count:
 prefill and decode tokens/s through ``InferenceEngine.generate`` (the scheduler, block manager and step function a
 user gets), random weights, a few layer sizes that resemble real models; plus device-timed runs of the design's own
 attention and expert kernels against the measured roofline, next to the GPT family's like kernels.
-``bench.py --arch-compare nafazen|teluzen|namisun`` prints the result as one JSON line.
+``bench.py --arch-compare nafazen|teluzen|namisun|tupidra`` prints the result as one JSON line.  Tupidra is also set beside
+Namisun (the other parallel-layout design with state slots) of equal width and depth, with both designs' like kernels.
 
 Reference: the reference's serving benchmark is ``llmctl bench e2e`` (reference llmctl/cli/commands/bench.py:98-160)."""
 from __future__ import annotations
@@ -41,6 +42,18 @@ NAMISUN_SIZES: Dict[str, Dict[str, Any]] = {
     "w2048": dict(width=2048, vocab=32000, pattern="MGAMGA", moe="1", loop=None, heads=16, kv_heads=4, dim=64, vdim=128, rot_dims=64,
                   rot_factor=8.0, gla_heads=16, gla_dim=64, gla_vdim=128, decay_rank=16, inner=4096, state=16, dt_rank=128, conv=4,
                   experts=6, identity=2, top=2, groups=(4, 2), ff=2048, limit=7.0),
+}
+
+
+TUPIDRA_SIZES: Dict[str, Dict[str, Any]] = {
+    # 6 layers: scan, soft-capped window attention (window 512 + 4 kept tokens), latent attention, twice; the second latent
+    # layer reads the first one's cache; a gated GELU feed-forward beside every mixer; input convolutions of 4 taps
+    "w1024": dict(width=1024, vocab=32000, pattern="MALMAc", ff="1", taps=4, heads=8, kv_heads=2, dim=128, vdim=128, softcap=30.0,
+                  window=512, keep_first=4, lat_heads=8, lat_dim=128, rot_dim=64, lat_vdim=128, kv_rank=512, q_rank=384, inner=2048,
+                  state=16, dt_rank=64, conv=4, ff_size=4096),
+    "w2048": dict(width=2048, vocab=32000, pattern="MALMAc", ff="1", taps=4, heads=16, kv_heads=4, dim=128, vdim=128, softcap=30.0,
+                  window=512, keep_first=4, lat_heads=16, lat_dim=128, rot_dim=64, lat_vdim=128, kv_rank=512, q_rank=768, inner=4096,
+                  state=16, dt_rank=128, conv=4, ff_size=8192),
 }
 
 
@@ -322,6 +335,133 @@ def _namisun_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str,
     return res
 
 
+def _tupidra_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
+    """The design's own kernels in isolation (bf16, L2 flushed before every call), each next to Namisun's like kernel at the
+    same token counts: soft-capped window attention against differential attention (prefill 2 x 2048 tokens; decode 32
+    sequences at context 4096), bias + value norm + append against rotation + append, residual + statistics and norm +
+    input convolution against the fused residual + layer norm, latent attention with sinks (Nafazen's kernels), the gated
+    GELU, and the selective scan both designs share."""
+    from ..ops import canon as C
+    from ..ops import diff_attention as DA
+    from ..ops import elementwise as E
+    from ..ops import latent_attention as L
+    from ..ops import native
+    from ..ops import recurrent as R
+    from ..ops import softcap_attention as SA
+    from ..ops.elementwise import rope_frequencies
+    from .ragged import Portion, RaggedBatch
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    H, G, d, e = size["heads"], size["kv_heads"], size["dim"], size["vdim"]
+    window, keep, cap = size["window"], size["keep_first"], size["softcap"]
+    LH, dn, dr, Rk = size["lat_heads"], size["lat_dim"], size["rot_dim"], size["kv_rank"]
+    Cn, N, Rdt, taps = size["inner"], size["state"], size["dt_rank"], size["conv"]
+    W, ctaps = size["width"], size["taps"]
+    bs, res = 64, {}
+    Wc = G * (d + e)
+    slopes, sinks = SA.distance_slopes(H).to(dev), torch.zeros(H, device=dev)
+    freq, mult = rope_frequencies(dr, 10000.0, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0})
+    freq = freq.to(dev)
+    # Namisun's differential attention at equal heads and key / value bytes per token: two maps of d / 2
+    nd, nWc = d // 2, G * (d + e)
+    nfreq, nmult = rope_frequencies(nd, 10000.0, {"factor": 8.0})
+    for name, nseq, ctx, new in (("prefill", 2, 2048, 2048), ("decode", 32, 4096, 1)):
+        per = (ctx + bs - 1) // bs
+        cache = torch.randn(nseq * per, bs, Wc, device=dev).to(bf)
+        ps = [Portion(i, [0] * new, ctx - new, [], list(range(i * per, (i + 1) * per)), i) for i in range(nseq)]
+        b = RaggedBatch(ps, bs, dev)
+        T = b.num_tokens
+        q = torch.randn(T, H * d, device=dev)
+        gate = torch.randn(T, H * e, device=dev).to(bf)
+        width = SA.tile_width(bf, H, G, d, e, True, new == 1)
+        tile_tokens = 1 if new == 1 else width
+        t = _time_flushed(lambda: SA.softcap_window_attention(q, cache, b.block_tables, b.tiles(width), tile_tokens, b.positions, gate, slopes,
+                                                              sinks, d ** -0.5, cap, window, keep, H, G, d, e, bs, bf, max_context=b.max_context))
+        seen = lambda i: min(i + 1, window) + max(min(keep, i + 1 - window), 0)
+        pairs = nseq * sum(seen(i) for i in range(ctx - new, ctx))                 # visible (query, key) pairs per head
+        flops = 2.0 * H * pairs * (d + e)
+        read_keys = nseq * (min(ctx, window + keep + (new - 1)))                    # cache rows a step must read
+        bytes_ = read_keys * Wc * 2 + T * H * (d * 4 + 2 * e * 2)
+        res[f"softcap_window_attention_{name}"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "gbs": bytes_ / t / 1e9,
+                                                   "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"],
+                                                   "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"],
+                                                   "tensor_cores": SA.uses_tensor_cores(bf, H, G, d, e, tile_tokens)}
+        # Namisun: differential attention, full causal context
+        nq = torch.randn(T, H * 2 * nd, device=dev)
+        ngate = torch.randn(T, H, device=dev).to(bf)
+        nwidth = DA.tile_width(bf, H, G, nd, e, True, new == 1)
+        ntile = 1 if new == 1 else nwidth
+        t = _time_flushed(lambda: DA.diff_attention(nq, cache, b.block_tables, b.tiles(nwidth), ntile, b.positions, ngate, nd ** -0.5, 0.5, 0.7,
+                                                    1e-5, H, G, nd, e, bs, bf, max_context=b.max_context))
+        npairs = nseq * sum(i + 1 for i in range(ctx - new, ctx))
+        nflops = 2.0 * H * npairs * (2 * nd + 2 * e)
+        nbytes = nseq * ctx * nWc * 2 + T * H * (2 * nd * 4 + e * 2)
+        res[f"namisun_diff_attention_{name}"] = {"ms": t * 1e3, "tflops": nflops / t / 1e12, "gbs": nbytes / t / 1e9,
+                                                 "frac_of_bf16_peak": nflops / t / 1e12 / peaks["bf16_tflops"],
+                                                 "frac_of_hbm": nbytes / t / 1e9 / peaks["hbm_gbs"]}
+        # latent attention with sinks
+        lcache = torch.randn(nseq * per, bs, Rk + dr, device=dev).to(bf)
+        ql = torch.randn(T, LH, Rk, device=dev)
+        lq = torch.randn(T, LH * (dn + dr), device=dev).to(bf)
+        rows = L.ROWS_PER_TILE_TCGEN05 if new > 1 and L.uses_tcgen05(bf, Rk, dr, bs, True) else L.rows_per_tile(bf, Rk, dr, True, LH if new == 1 else 32)
+        if L.uses_tensor_cores(bf, Rk, dr):
+            ql = ql.to(bf)
+        lsinks = torch.randn(LH, device=dev)
+        for label, sk in (("latent_attention_sinks", lsinks), ("nafazen_latent_attention", None)):
+            t = _time_flushed(lambda: L.latent_attention(ql, lq, dn, lcache, b.block_tables, b.tiles(rows), b.positions, freq, mult, 0.07,
+                                                         b.heads_per_tile(LH, rows), b.max_context, b.attention_splits(LH, rows), rows=rows, sinks=sk))
+            keys = nseq * (ctx * new - new * (new - 1) // 2)
+            flops = 2.0 * LH * keys * (2 * Rk + dr)
+            bytes_ = nseq * ctx * (Rk + dr) * 2 + T * LH * (Rk * ql.element_size() + Rk * 2)
+            res[f"{label}_{name}"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "gbs": bytes_ / t / 1e9,
+                                      "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"], "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
+        # selective scan (shared with Namisun)
+        xz = torch.randn(T, 2 * Cn, device=dev).to(bf)
+        u = torch.randn(T, Cn, device=dev).to(bf)
+        bc = torch.randn(T, Rdt + 2 * N, device=dev).to(bf)
+        dtp = torch.randn(T, Cn, device=dev).to(bf)
+        dtb, A, D = torch.randn(Cn, device=dev) - 1.0, -torch.exp(torch.randn(Cn, N, device=dev)), torch.randn(Cn, device=dev)
+        sst, cst = torch.zeros(nseq, Cn, N, device=dev), torch.zeros(nseq, taps - 1, Cn, device=dev)
+        t = _time_flushed(lambda: R.selective_scan(u, bc, Rdt, Rdt + N, dtp, dtb, A, D, xz[:, Cn:], xz[:, :Cn], b.portions, sst, cst))
+        bytes_ = T * (4 * Cn * 2 + 2 * N * 2) + 2 * sst.numel() * 4
+        res[f"selective_scan_{name}"] = {"ms": t * 1e3, "gbs": bytes_ / t / 1e9, "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
+        # the layer's glue: residual + statistics, norm + input convolution for both sublayers; Namisun: residual + layer norm
+        x = torch.randn(T, W, device=dev)
+        a, f = torch.randn(T, W, device=dev).to(bf), torch.randn(T, W, device=dev).to(bf)
+        nw = [torch.ones(W, device=dev), torch.ones(W, device=dev)]
+        cw = [torch.randn(W, ctaps, device=dev), torch.randn(W, ctaps, device=dev)]
+        cstate = torch.zeros(nseq, ctaps - 1, W, device=dev)
+        r = C.residual_rms(None, None, x, 1e-6)
+        t1 = _time_flushed(lambda: C.residual_rms(a, f, x, 1e-6))
+        t2 = _time_flushed(lambda: C.norm_canon(x, r, nw, cw, b.portions, b.seq_rows, cstate, bf))
+        bytes_ = T * W * (2 + 2 + 4 + 4) + T * W * (4 + 2 + 2)
+        res[f"residual_norm_canon_{name}"] = {"ms": (t1 + t2) * 1e3, "ms_residual": t1 * 1e3, "ms_norm_canon": t2 * 1e3,
+                                              "gbs": bytes_ / (t1 + t2) / 1e9, "frac_of_hbm": bytes_ / (t1 + t2) / 1e9 / peaks["hbm_gbs"]}
+        f32, w1, b1 = torch.randn(T, W, device=dev), torch.ones(W, device=dev), torch.zeros(W, device=dev)
+        t = _time_flushed(lambda: E.parallel_residual(a, f32, x, 0.5, 1e-5, bf, w1, b1, want_fp32=True))
+        bytes_ = T * W * (2 + 4 + 4 + 4 + 2 + 4)
+        res[f"namisun_residual_norm_{name}"] = {"ms": t * 1e3, "gbs": bytes_ / t / 1e9, "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
+        if new > 1:
+            proj = torch.randn(T, H * d + Wc + H * e, device=dev).to(bf)
+            bias = torch.randn(H * d + Wc, device=dev)
+            t = _time_flushed(lambda: SA.window_kv_append(proj, bias, H, G, d, e, True, 1e-6, b.slots, cache))
+            bytes_ = T * ((H * d + Wc) * 2 + H * d * 4 + Wc * 2)
+            res["window_kv_append_prefill"] = {"ms": t * 1e3, "gbs": bytes_ / t / 1e9, "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
+            nproj = torch.randn(T, H * 2 * nd + nWc + H, device=dev).to(bf)
+            t = _time_flushed(lambda: DA.rotary_kv_append(nproj, 2 * H, 2 * G, nd, G * e, nd, nfreq.to(dev), nmult, b.positions, b.slots, cache))
+            bytes_ = T * ((H * 2 * nd + nWc) * 2 + H * 2 * nd * 4 + nWc * 2)
+            res["namisun_rotary_kv_append_prefill"] = {"ms": t * 1e3, "gbs": bytes_ / t / 1e9, "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
+            F = size["ff_size"]
+            gu = torch.randn(T, 2 * F, device=dev).to(bf)
+            t = _time_flushed(lambda: E.gated_gelu_tanh(gu))
+            t_silu = _time_flushed(lambda: E.gated_silu(gu))
+            res["gated_gelu_prefill"] = {"ms": t * 1e3, "gbs": T * F * 6 / t / 1e9, "frac_of_hbm": T * F * 6 / t / 1e9 / peaks["hbm_gbs"],
+                                         "gated_silu_ms": t_silu * 1e3}
+    res.update(_gpt_kernels(dict(size, top=1, expert_ff=size["ff_size"]), peaks))
+    res["native_launches"] = native.launch_count
+    return res
+
+
 def _gpt_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
     """The GPT family's like kernels at like sizes: causal flash attention over the same 2 x 2048 tokens, paged decode
     attention over the same 32 contexts of 4096 (head size 128 for both), and the SwiGLU feed-forward's two GEMMs on
@@ -365,6 +505,9 @@ def run(which: str = "nafazen", sizes: List[str] | None = None, prompt_len: int 
     elif which == "namisun":
         from ..models.namisun import NamisunConfig as Config, example_config
         table, kernels = NAMISUN_SIZES, _namisun_kernels
+    elif which == "tupidra":
+        from ..models.tupidra import TupidraConfig as Config, example_config
+        table, kernels = TUPIDRA_SIZES, _tupidra_kernels
     else:
         raise ValueError(f"no architecture comparison for {which!r}")
     peaks = _peaks()
@@ -381,6 +524,11 @@ def run(which: str = "nafazen", sizes: List[str] | None = None, prompt_len: int 
         row = {"params": params, "gpt_params": gcfg.num_parameters(), "gpt_ffn": gcfg.ffn,
                which: _serve(ncfg, prompts, new_tokens, 64), "gpt": _serve(gcfg, prompts, new_tokens, 16),
                "kernels": kernels(size, peaks)}
+        if which == "tupidra" and name in NAMISUN_SIZES:          # the closest design: parallel layout, scans, state slots
+            from ..models.namisun import NamisunConfig, example_config as namisun_example
+            ccfg = NamisunConfig.from_dict(namisun_example(**NAMISUN_SIZES[name]), name=f"namisun-{name}")
+            row["namisun_params"] = ccfg.num_parameters()
+            row["namisun"] = _serve(ccfg, prompts, new_tokens, 64)
         row["seconds"] = round(time.time() - t0, 1)
         out["sizes"][name] = row
     return out

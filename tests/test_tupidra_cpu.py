@@ -156,7 +156,7 @@ def test_window_attention_alone(H, G, d, e, n, bs, window, keep, cap):
     kb = k.double() + bias[nq:nq + nk].view(G, d).double()
     vb = oracle.rms(v.double() + bias[nq + nk:].view(G, e).double(), 1e-4)
     assert torch.allclose(qo.double(), qb.reshape(n, -1), atol=1e-6)
-    want = oracle.window_core(qb, kb, vb, 0.4, cap if cap else 1e30, window if window else 10 ** 9, keep)
+    want = oracle.window_core(qb, kb, vb, 0.4, cap, window, keep)
     gate = torch.randn(n, H * e)
     for width in (1, 16):
         tiles = torch.tensor([[s, min(width, n - s), 0, 0] for s in range(0, n, width)], dtype=torch.int32)

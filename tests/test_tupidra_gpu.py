@@ -144,9 +144,10 @@ def test_window_edges_decide_on_every_kernel(cuda_device, bs, window, keep, d, e
                                                  torch.zeros(H, device=dev), 1.0, cap, window, keep, H, G, d, e, bs, dt, max_context=n,
                                                  splits=splits, tensor_cores=tc).float().cpu()
                 assert torch.allclose(out.double(), want, atol=1e-4 if dt == torch.float32 else 3e-2), (star, dt, width, tc)
-                assert torch.allclose(out[last_seen, :3], v[star, 0, :3], atol=2e-2)
+                # head 1 has the small slope (2^-8 a position): the distance bias leaves the dominant key dominant
+                assert torch.allclose(out[last_seen, e:e + 3], v[star, 0, :3], atol=3e-2)
                 if last_seen + 1 < n:
-                    assert (out[last_seen + 1, :3] - v[star, 0, :3]).abs().max() > 0.5
+                    assert (out[last_seen + 1, e:e + 3] - v[star, 0, :3]).abs().max() > 0.5
 
 
 @pytest.mark.parametrize("H,dn,dr,R,n,bs,far", [(3, 6, 4, 16, 70, 8, 0), (4, 16, 16, 48, 200, 64, 63), (8, 16, 64, 64, 300, 64, 64),

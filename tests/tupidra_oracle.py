@@ -106,7 +106,8 @@ def latent_attention(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict[str, A
 
 
 def window_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, cap: float, size: int, keep: int) -> torch.Tensor:
-    """q: [T, H, d]; k: [T, G, d]; v: [T, G, e] (already at unit RMS).  Returns [T, H, e]."""
+    """q: [T, H, d]; k: [T, G, d]; v: [T, G, e] (already at unit RMS).  Returns [T, H, e].  A configuration without a cap
+    or without a window has none (cap / size 0 or None)."""
     T, H = q.shape[0], q.shape[1]
     G, e = k.shape[1], v.shape[2]
     out = torch.zeros(T, H, e, dtype=F64)
@@ -116,9 +117,11 @@ def window_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
             slope = 2.0 ** (-8.0 * (hd + 1) / H)
             den, acc = 1.0, torch.zeros(e, dtype=F64)
             for j in range(i + 1):
-                if i - j < size or j < keep:
+                if not size or i - j < size or j < keep:
                     s = float(q[i, hd] @ k[j, g]) * scale
-                    s = cap * math.tanh(s / cap) - slope * (i - j)
+                    if cap:
+                        s = cap * math.tanh(s / cap)
+                    s -= slope * (i - j)
                     w = math.exp(s)
                     den += w
                     acc += w * v[j, g]
@@ -133,7 +136,8 @@ def window_attention(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict[str, A
     k = (h @ P["k"].T + P["k.b"]).view(T, G, d)
     v = rms((h @ P["v"].T + P["v.b"]).view(T, G, e), eps)
     gate = torch.sigmoid(h @ P["g"].T).view(T, H, e)
-    out = window_core(q, k, v, m["scale"], m["softcap"], m["mask"]["size"], m["mask"]["keep_first"])
+    mask = m.get("mask") or {}
+    out = window_core(q, k, v, m["scale"], m.get("softcap"), mask.get("size"), mask.get("keep_first") or 0)
     return (out * gate).reshape(T, H * e) @ P["o"].T + P["o.b"]
 
 
