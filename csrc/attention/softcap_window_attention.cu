@@ -349,7 +349,7 @@ __device__ __forceinline__ float sw_tanh(float x) {
 // NT: n-tiles of 8 output columns (e <= 8 NT).  decode = 0: rows of the CTA are the tile's tokens (head blockIdx.y);
 // decode = 1: rows are HB heads of the tile's single token.
 template <int NT, bool SPLIT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, SPLIT ? 1 : 2)
 softcap_attention_mma_kernel(const SoftcapAttnParams p, int decode) {
   extern __shared__ __align__(16) unsigned char sw_smem[];
   const int H = p.H, G = p.G, d = p.d, e = p.e, bs = p.bs;
@@ -372,20 +372,23 @@ softcap_attention_mma_kernel(const SoftcapAttnParams p, int decode) {
 
   {
     const int per_row = d >> 2;
-    for (int i = tid; i < rows_cta * per_row; i += nthreads) {
+    for (int i = tid; i < nvalid * per_row; i += nthreads) {
       const int r = i / per_row, c = (i % per_row) << 2;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (r < nvalid) {
-        const long long tok = decode ? t0 : t0 + r;
-        const int head = decode ? h0 + r : h0;
-        v = *reinterpret_cast<const float4*>(p.q + (tok * H + head) * d + c);
-        v.x *= p.scale, v.y *= p.scale, v.z *= p.scale, v.w *= p.scale;
-      }
+      const long long tok = decode ? t0 : t0 + r;
+      const int head = decode ? h0 + r : h0;
+      float4 v = *reinterpret_cast<const float4*>(p.q + (tok * H + head) * d + c);
+      v.x *= p.scale, v.y *= p.scale, v.z *= p.scale, v.w *= p.scale;
       uint32_t h01, l01, h23, l23;
       sw_split_pack(v.x, v.y, h01, l01);
       sw_split_pack(v.z, v.w, h23, l23);
       *reinterpret_cast<uint2*>(Qhi + r * ldq + c) = make_uint2(h01, h23);
       *reinterpret_cast<uint2*>(Qlo + r * ldq + c) = make_uint2(l01, l23);
+    }
+    const int per_row8 = d >> 3;                 // rows without a query: zeros (16 bytes at a time; ldq is a multiple of 8)
+    for (int i = tid; i < (rows_cta - nvalid) * per_row8; i += nthreads) {
+      const int r = nvalid + i / per_row8, c = (i % per_row8) << 3;
+      *reinterpret_cast<uint4*>(Qhi + r * ldq + c) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(Qlo + r * ldq + c) = make_uint4(0u, 0u, 0u, 0u);
     }
   }
 

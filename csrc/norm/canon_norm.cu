@@ -13,6 +13,8 @@
 //       sequence's state slot ([slots, taps - 1, W] fp32, the unweighted n of the last taps - 1 positions, oldest first;
 //       a portion that starts at position 0 reads zeros whatever the slot holds).  A second launch then stores the new
 //       last rows: the first one only reads the state, so no block can see a row of the step it is in.
+//   llmctl_residual_norm_canon_small : all of it in one launch, one block per portion, for batches of short portions
+//       (decoding: a step is bound by its launches, not by bytes).
 // Everything is fp32 up to the rounding of out_s to the activation type.
 // Reference: none (the reference has no model code).
 #include "../common/dtype.cuh"
@@ -46,6 +48,7 @@ residual_rms_kernel(const void* __restrict__ a, int a32, long long lda, const vo
 }
 
 constexpr int kCanonMaxTaps = 8;
+constexpr int kCanonChunk = 8;      // most consecutive tokens a thread of the vector kernel walks
 
 struct CanonParams {
   const float* x;            // [T, W]
@@ -104,6 +107,110 @@ norm_canon_kernel(const CanonParams p) {
   }
 }
 
+// Vector path (W a multiple of 4): a thread owns four neighbouring channels of `tokens_per_cta` consecutive tokens and
+// keeps the last TAPS - 1 normed rows in registers, so every row of x is read once; the window is rebuilt from the step's
+// earlier rows or from the state slot at the block's first token and wherever a portion starts.
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(256)
+norm_canon_vec_kernel(const CanonParams p, int tokens, int tokens_per_cta) {
+  constexpr int KEEP = TAPS - 1;
+  const int W = p.W, W4 = W >> 2;
+  const int t_begin = blockIdx.x * tokens_per_cta, t_end = min(tokens, t_begin + tokens_per_cta);
+  for (int c4 = blockIdx.y * blockDim.x + threadIdx.x; c4 < W4; c4 += gridDim.y * blockDim.x) {
+    const int c = c4 << 2;
+    float cw[2][4][TAPS];
+    float4 nw[2];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      nw[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (s < p.S) {
+        nw[s] = *reinterpret_cast<const float4*>(p.norm_w[s] + c);
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+          for (int j = 0; j < TAPS; ++j) cw[s][ch][j] = p.conv_w[s][static_cast<long long>(c + ch) * TAPS + j];
+      }
+    }
+    // all rows of the chunk are requested before the first one is used
+    float4 rows[kCanonChunk];
+    float rr[kCanonChunk];
+#pragma unroll
+    for (int k = 0; k < kCanonChunk; ++k) {
+      rows[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      rr[k] = 0.f;
+      if (t_begin + k < t_end) {
+        rows[k] = *reinterpret_cast<const float4*>(p.x + static_cast<long long>(t_begin + k) * W + c);
+        rr[k] = p.r[t_begin + k];
+      }
+    }
+    float4 win[KEEP > 0 ? KEEP : 1];
+#pragma unroll
+    for (int k = 0; k < kCanonChunk; ++k) {
+      const int t = t_begin + k;
+      if (t >= t_end) break;
+      const int* pr = p.portions + 4 * p.seq_rows[t];
+      const int i = t - pr[0];
+      if (k == 0 || i == 0) {
+        const bool has_state = pr[2] > 0 && pr[3] >= 0;
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+          const int off = i - KEEP + j;
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (off >= 0) {
+            v = *reinterpret_cast<const float4*>(p.x + static_cast<long long>(t - KEEP + j) * W + c);
+            const float rv = p.r[t - KEEP + j];
+            v.x *= rv, v.y *= rv, v.z *= rv, v.w *= rv;
+          } else if (has_state) {
+            v = *reinterpret_cast<const float4*>(p.state + (static_cast<long long>(pr[3]) * KEEP + i + j) * W + c);
+          }
+          win[j] = v;
+        }
+      }
+      float4 cur = rows[k];
+      cur.x *= rr[k], cur.y *= rr[k], cur.z *= rr[k], cur.w *= rr[k];
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        if (s < p.S) {
+          float o[4] = {cur.x * (1.f + cw[s][0][KEEP]), cur.y * (1.f + cw[s][1][KEEP]), cur.z * (1.f + cw[s][2][KEEP]),
+                        cur.w * (1.f + cw[s][3][KEEP])};
+#pragma unroll
+          for (int j = 0; j < KEEP; ++j) {
+            o[0] += cw[s][0][j] * win[j].x;
+            o[1] += cw[s][1][j] * win[j].y;
+            o[2] += cw[s][2][j] * win[j].z;
+            o[3] += cw[s][3][j] * win[j].w;
+          }
+          o[0] *= nw[s].x, o[1] *= nw[s].y, o[2] *= nw[s].z, o[3] *= nw[s].w;
+          T* dst = static_cast<T*>(p.out[s]) + static_cast<long long>(t) * W + c;
+          if constexpr (sizeof(T) == 4) {
+            *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+          } else {
+            *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j + 1 < KEEP; ++j) win[j] = win[j + 1];
+      if (KEEP > 0) win[KEEP > 0 ? KEEP - 1 : 0] = cur;
+    }
+  }
+}
+
+template <typename T>
+static void launch_norm_canon_vec(const CanonParams& p, int tokens, cudaStream_t s) {
+  // about two waves of blocks; long chunks amortise the window's rebuild, short ones keep small batches parallel
+  const int per = max(1, min(kCanonChunk, tokens / (2 * kNumSMs)));
+  const int W4 = p.W >> 2;
+  const dim3 grid((tokens + per - 1) / per, (W4 + 255) / 256);
+  const int threads = W4 >= 256 ? 256 : ((W4 + 31) / 32) * 32;
+  switch (p.taps) {
+#define LLMCTL_CANON_CASE(N) case N: norm_canon_vec_kernel<T, N><<<grid, threads, 0, s>>>(p, tokens, per); break;
+    LLMCTL_CANON_CASE(1) LLMCTL_CANON_CASE(2) LLMCTL_CANON_CASE(3) LLMCTL_CANON_CASE(4)
+    LLMCTL_CANON_CASE(5) LLMCTL_CANON_CASE(6) LLMCTL_CANON_CASE(7) LLMCTL_CANON_CASE(8)
+#undef LLMCTL_CANON_CASE
+  }
+}
+
 // One block per portion: the slot's new rows are the last taps - 1 normed rows of the sequence, taken from the step's
 // rows and, for portions shorter than that, from the slot's own later rows.
 __global__ void __launch_bounds__(256)
@@ -130,6 +237,58 @@ canon_state_store_kernel(const CanonParams p) {
   }
 }
 
+// Small portions (each at most kCanonChunk tokens: a decoding batch): one block per portion does the residual update, the
+// statistics, the sublayers' inputs and the slot's new rows in a single launch.  A thread owns the channels c, c + 256, ...
+// through all phases, so it only ever rereads what it wrote itself; the rows' statistics cross the block once.
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_norm_canon_small_kernel(const void* __restrict__ a, int a32, long long lda, const void* __restrict__ f, int f32, long long ldf,
+                                 float* __restrict__ x, float eps, const CanonParams p) {
+  __shared__ float red[32];
+  __shared__ float rr[kCanonChunk];
+  const int* pr = p.portions + 4 * blockIdx.x;
+  const int t0 = pr[0], n = min(pr[1], kCanonChunk), pos0 = pr[2], slot = pr[3];
+  if (n <= 0) return;
+  const int W = p.W, taps = p.taps, keep = taps - 1;
+  for (int k = 0; k < n; ++k) {
+    const long long t = t0 + k;
+    float* row = x + t * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      float v = row[c];
+      if (a != nullptr || f != nullptr) {
+        float sum = 0.f;
+        if (a != nullptr) sum = load_any(a, a32, t * lda + c);
+        if (f != nullptr) sum += load_any(f, f32, t * ldf + c);
+        v += sum;
+        row[c] = v;
+      }
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) rr[k] = 1.f / sqrtf(ss / static_cast<float>(W) + eps);
+  }
+  __syncthreads();
+  const bool has_state = pos0 > 0 && slot >= 0;
+  float* st = slot >= 0 && keep > 0 ? p.state + static_cast<long long>(slot) * keep * W : nullptr;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float nb[kCanonMaxTaps - 1 + kCanonChunk];          // normed values at offsets -keep .. n - 1 of the portion
+    for (int m = 0; m < keep; ++m) nb[m] = has_state ? st[static_cast<long long>(m) * W + c] : 0.f;
+    for (int k = 0; k < n; ++k) nb[keep + k] = x[static_cast<long long>(t0 + k) * W + c] * rr[k];
+    for (int s = 0; s < p.S; ++s) {
+      const float* cw = p.conv_w[s] + static_cast<long long>(c) * taps;
+      const float nw = p.norm_w[s][c];
+      for (int k = 0; k < n; ++k) {
+        float acc = nb[keep + k];
+        for (int j = 0; j < taps; ++j) acc += cw[j] * nb[k + j];
+        static_cast<T*>(p.out[s])[static_cast<long long>(t0 + k) * W + c] = from_f32<T>(acc * nw);
+      }
+    }
+    if (st != nullptr)
+      for (int m = 0; m < keep; ++m) st[static_cast<long long>(m) * W + c] = nb[n + m];
+  }
+}
+
 }  // namespace llmctl
 
 using namespace llmctl;
@@ -152,7 +311,28 @@ LLMCTL_API int llmctl_norm_canon(const float* x, const float* r, int S, const fl
   if (tokens == 0) return 0;
   CanonParams p{x, r, {norm_w0, norm_w1}, {conv_w0, conv_w1}, {out0, out1}, portions, seq_rows, state, S, W, taps};
   cudaStream_t s = (cudaStream_t)stream;
-  LLMCTL_DISPATCH_DTYPE(out_is_fp32, T, (norm_canon_kernel<T><<<tokens, 256, 0, s>>>(p)));
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out0) | reinterpret_cast<uintptr_t>(out1) |
+                         reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(norm_w0) | reinterpret_cast<uintptr_t>(norm_w1)) & 15) == 0;
+  if (W % 4 == 0 && aligned) {
+    LLMCTL_DISPATCH_DTYPE(out_is_fp32, T, (launch_norm_canon_vec<T>(p, tokens, s)));
+  } else {
+    LLMCTL_DISPATCH_DTYPE(out_is_fp32, T, (norm_canon_kernel<T><<<tokens, 256, 0, s>>>(p)));
+  }
   if (taps > 1 && nportions > 0) canon_state_store_kernel<<<nportions, 256, 0, s>>>(p);
+  LLMCTL_RETURN_LAST();
+}
+
+// The three steps above in one launch for batches whose portions have at most 8 tokens each (decoding): x += a + f, the
+// statistics, out_s and the state's new rows; one block per portion.
+LLMCTL_API int llmctl_residual_norm_canon_small(const void* a, int a_is_fp32, long long lda, const void* f, int f_is_fp32, long long ldf,
+                                                float* x, float eps, int S, const float* norm_w0, const float* conv_w0, void* out0,
+                                                const float* norm_w1, const float* conv_w1, void* out1, const int* portions,
+                                                int nportions, float* state, int W, int taps, int out_is_fp32, void* stream) {
+  LLMCTL_BEGIN();
+  LLMCTL_REQUIRE((S == 1 || S == 2) && taps >= 1 && taps <= kCanonMaxTaps && W > 0 && (taps == 1 || state != nullptr) && x != nullptr);
+  if (nportions == 0) return 0;
+  CanonParams p{x, nullptr, {norm_w0, norm_w1}, {conv_w0, conv_w1}, {out0, out1}, portions, nullptr, state, S, W, taps};
+  LLMCTL_DISPATCH_DTYPE(out_is_fp32, T, (residual_norm_canon_small_kernel<T><<<nportions, 256, 0, (cudaStream_t)stream>>>(
+                                            a, a_is_fp32, lda, f, f_is_fp32, ldf, x, eps, p)));
   LLMCTL_RETURN_LAST();
 }

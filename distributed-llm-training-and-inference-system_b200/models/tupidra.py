@@ -218,12 +218,18 @@ class TupidraModel(nn.Module):
         """``batch``: serve.ragged.RaggedBatch.  Returns fp32 logits [len(batch.out_rows), vocab]."""
         cfg, dt, eps = self.cfg, self.dtype, self.cfg.norm_eps
         x, _ = eops.embed_scale(batch.tokens, self.embed, 1.0)
-        r = cops.residual_rms(None, None, x, eps)
-        for blk, (canon_state, own) in zip(self.blocks, caches):
-            hs = cops.norm_canon(x, r, list(blk.norm_w), list(blk.canon_w), batch.portions, batch.seq_rows, canon_state, dt)
+        small = batch.decode_only               # one token per portion: the layer's glue is a single launch
+        a = f = None
+        for i, blk in enumerate(self.blocks):
+            canon_state, own = caches[i]
+            # the previous layer's residual update (x += a + f), this layer's norm statistics and both sublayers' inputs
+            hs = cops.residual_norm_canon(a, f, x, eps, list(blk.norm_w), list(blk.canon_w), batch.portions, batch.seq_rows, canon_state, dt, small)
+            if layer_trace is not None and i > 0:
+                layer_trace.append(x.clone())
             a = blk.mixer(hs[0], batch, own)
             f = blk.mlp(hs[1]) if blk.mlp is not None else None
-            r = cops.residual_rms(a, f, x, eps)             # x += a + f, and the statistics of the next norm
+        if a is not None:
+            cops.residual_rms(a, f, x, eps)
             if layer_trace is not None:
                 layer_trace.append(x.clone())
         if batch.num_out == 0:                  # a step that only fills the caches and states

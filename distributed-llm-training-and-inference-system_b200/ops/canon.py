@@ -24,8 +24,12 @@ native.register_signature("llmctl_residual_rms", [c_void_p, c_int, c_ll, c_void_
 native.register_signature("llmctl_norm_canon", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                  c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
 native._KERNELS_PER_CALL["llmctl_norm_canon"] = 2
+native.register_signature("llmctl_residual_norm_canon_small", [c_void_p, c_int, c_ll, c_void_p, c_int, c_ll, c_void_p, c_float, c_int, c_void_p,
+                                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                                c_int, c_int, c_int, c_void_p])
 
 MAX_TAPS = 8
+SMALL_PORTION = 8       # portions of at most this many tokens each can take the single-launch path
 
 
 def residual_rms(a: Optional[torch.Tensor], f: Optional[torch.Tensor], x: torch.Tensor, eps: float) -> torch.Tensor:
@@ -79,3 +83,25 @@ def norm_canon(x: torch.Tensor, r: torch.Tensor, norm_w: Sequence[torch.Tensor],
         if slot >= 0 and keep:
             state[slot] = rows[-keep:]
     return [o.to(out_dtype) for o in outs]
+
+
+def residual_norm_canon(a: Optional[torch.Tensor], f: Optional[torch.Tensor], x: torch.Tensor, eps: float, norm_w: Sequence[torch.Tensor],
+                        conv_w: Sequence[torch.Tensor], portions: torch.Tensor, seq_rows: torch.Tensor, state: torch.Tensor,
+                        out_dtype: torch.dtype, small: bool = False) -> List[torch.Tensor]:
+    """``residual_rms`` followed by ``norm_canon``: the end of one layer and the start of the next.  ``small``: every portion
+    has at most ``SMALL_PORTION`` tokens (a decoding batch) — on a GPU the whole step is then one launch."""
+    if small and x.is_cuda:
+        T, W = x.shape
+        S, taps = len(norm_w), conv_w[0].shape[1]
+        assert x.dtype == torch.float32 and x.is_contiguous() and state.is_contiguous() and S in (1, 2) and 1 <= taps <= MAX_TAPS
+        for t in (a, f):
+            assert t is None or (t.shape == x.shape and t.stride(1) == 1)
+        outs = [torch.empty(T, W, dtype=out_dtype, device=x.device) for _ in range(S)]
+        native.call("llmctl_residual_norm_canon_small", native.ptr(a), _is32(a) if a is not None else 0, a.stride(0) if a is not None else 0,
+                    native.ptr(f), _is32(f) if f is not None else 0, f.stride(0) if f is not None else 0, x.data_ptr(), float(eps), S,
+                    norm_w[0].data_ptr(), conv_w[0].data_ptr(), outs[0].data_ptr(), native.ptr(norm_w[1]) if S > 1 else None,
+                    native.ptr(conv_w[1]) if S > 1 else None, outs[1].data_ptr() if S > 1 else None, portions.data_ptr(),
+                    portions.shape[0], state.data_ptr() if taps > 1 else None, W, taps, int(out_dtype == torch.float32), native.stream_ptr())
+        return outs
+    r = residual_rms(a, f, x, eps)
+    return norm_canon(x, r, norm_w, conv_w, portions, seq_rows, state, out_dtype)

@@ -349,6 +349,11 @@ int llmctl_residual_rms(const void* a, int a_is_fp32, long long lda, const void*
 int llmctl_norm_canon(const float* x, const float* r, int S, const float* norm_w0, const float* conv_w0, void* out0,
                       const float* norm_w1, const float* conv_w1, void* out1, const int* portions, int nportions,
                       const int* seq_rows, float* state, int tokens, int W, int taps, int out_is_fp32, void* stream);
+/* llmctl_residual_rms + llmctl_norm_canon in one launch for portions of at most 8 tokens each (one block per portion). */
+int llmctl_residual_norm_canon_small(const void* a, int a_is_fp32, long long lda, const void* f, int f_is_fp32, long long ldf, float* x,
+                                     float eps, int S, const float* norm_w0, const float* conv_w0, void* out0, const float* norm_w1,
+                                     const float* conv_w1, void* out1, const int* portions, int nportions, float* state, int W, int taps,
+                                     int out_is_fp32, void* stream);
 int llmctl_gated_gelu_tanh(const void* gate_up, long long ld, void* out, int is_fp32, int rows, int F, void* stream);
 int llmctl_sigmoid_gate(void* y, const void* z, long long ldz, int is_fp32, int rows, int F, void* stream);
 /* fp32 biases (or null), optional unit-RMS norm of every value head; q -> fp32, [k | v] -> cache row. */

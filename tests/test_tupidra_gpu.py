@@ -47,6 +47,37 @@ def test_input_convolution_kernels(cuda_device, W, taps, cuts):
         assert len(h1) == 1
 
 
+@pytest.mark.parametrize("W,taps", [(10, 4), (1000, 3), (4096, 8), (64, 1), (48, 2)])
+def test_single_launch_glue_for_short_portions(cuda_device, W, taps):
+    """Decoding batches: residual update, statistics, both inputs and the new state rows in one launch per layer, for three
+    sequences side by side (portions of 1-8 tokens, one at position 0 over a slot that holds garbage, one without a slot)."""
+    from llmctl_b200.ops import canon as C
+    torch.manual_seed(W + taps)
+    dev = cuda_device
+    nw = [torch.rand(W) + 0.5, torch.rand(W) + 0.5]
+    cw = [torch.randn(W, taps), torch.randn(W, taps)]
+    for dt in (torch.float32, torch.bfloat16):
+        sc = torch.randn(4, taps - 1, W)
+        sg = sc.clone().to(dev)
+        pos = [5, 0, 9]
+        for lens in ([1, 1, 1], [8, 3, 2], [2, 1, 5], [1, 1, 1]):
+            T = sum(lens)
+            x, a, f = torch.randn(T, W) * 2, torch.randn(T, W).to(dt), torch.randn(T, W).to(dt)
+            starts = [0, lens[0], lens[0] + lens[1]]
+            portions = torch.tensor([[starts[i], lens[i], pos[i], (2, 0, -1)[i]] for i in range(3)], dtype=torch.int32)
+            rows = torch.tensor(sum(([i] * lens[i] for i in range(3)), []), dtype=torch.int32)
+            xc, xg = x.clone(), x.clone().to(dev)
+            hc = C.residual_norm_canon(a, f, xc, 1e-5, nw, cw, portions, rows, sc, dt)
+            hg = C.residual_norm_canon(a.to(dev), f.to(dev), xg, 1e-5, [w.to(dev) for w in nw], [w.to(dev) for w in cw], portions.to(dev),
+                                       rows.to(dev), sg, dt, small=True)
+            assert torch.allclose(xg.cpu(), xc, atol=1e-6) and torch.allclose(sg.cpu(), sc, atol=1e-5)
+            for s in range(2):
+                assert hg[s].dtype == dt and torch.allclose(hg[s].float().cpu(), hc[s].float(), atol=1e-4 if dt == torch.float32 else 0.1, rtol=1e-2)
+            pos = [pos[i] + lens[i] for i in range(3)]
+        h1 = C.residual_norm_canon(None, None, xg, 1e-5, [nw[0].to(dev)], [cw[0].to(dev)], portions.to(dev), rows.to(dev), sg, dt, small=True)
+        assert len(h1) == 1
+
+
 def test_activation_kernels(cuda_device):
     from llmctl_b200.ops import elementwise as E
     torch.manual_seed(0)
