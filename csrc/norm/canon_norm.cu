@@ -237,19 +237,97 @@ canon_state_store_kernel(const CanonParams p) {
   }
 }
 
+// One token per portion and the whole row in one pass of the block (W / 4 <= threads): a thread owns four neighbouring
+// channels, asks for the slot's rows and the weights before the row's statistics are known, and finishes from registers.
+template <typename T, int TAPS>
+__device__ __forceinline__ void residual_norm_canon_one_token(const void* __restrict__ a, int a32, long long lda, const void* __restrict__ f,
+                                                              int f32, long long ldf, float* __restrict__ x, float eps, const CanonParams& p,
+                                                              long long t, int pos0, int slot, float* red) {
+  constexpr int KEEP = TAPS - 1;
+  const int W = p.W, c = threadIdx.x << 2;
+  const bool active = c < W;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 win[KEEP > 0 ? KEEP : 1];
+  float4 nw[2];
+  float* st = slot >= 0 && KEEP > 0 ? p.state + static_cast<long long>(slot) * KEEP * W : nullptr;
+  if (active) {
+    v = *reinterpret_cast<const float4*>(x + t * W + c);
+    float add[4] = {0.f, 0.f, 0.f, 0.f};
+    if (a != nullptr)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) add[k] = load_any(a, a32, t * lda + c + k);
+    if (f != nullptr)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) add[k] += load_any(f, f32, t * ldf + c + k);
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j)
+      win[j] = (st != nullptr && pos0 > 0) ? *reinterpret_cast<const float4*>(st + static_cast<long long>(j) * W + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+      if (s < p.S) nw[s] = *reinterpret_cast<const float4*>(p.norm_w[s] + c);
+    if (a != nullptr || f != nullptr) {
+      v.x += add[0], v.y += add[1], v.z += add[2], v.w += add[3];
+      *reinterpret_cast<float4*>(x + t * W + c) = v;
+    }
+  }
+  const float ss = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red);
+  if (!active) return;
+  const float r = 1.f / sqrtf(ss / static_cast<float>(W) + eps);
+  const float4 cur = make_float4(v.x * r, v.y * r, v.z * r, v.w * r);
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    if (s < p.S) {
+      float cw[4][TAPS];          // the same few kilobytes for every block: they come from the cache
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) cw[ch][j] = p.conv_w[s][static_cast<long long>(c + ch) * TAPS + j];
+      float o[4] = {cur.x * (1.f + cw[0][KEEP]), cur.y * (1.f + cw[1][KEEP]), cur.z * (1.f + cw[2][KEEP]), cur.w * (1.f + cw[3][KEEP])};
+#pragma unroll
+      for (int j = 0; j < KEEP; ++j) {
+        o[0] += cw[0][j] * win[j].x;
+        o[1] += cw[1][j] * win[j].y;
+        o[2] += cw[2][j] * win[j].z;
+        o[3] += cw[3][j] * win[j].w;
+      }
+      o[0] *= nw[s].x, o[1] *= nw[s].y, o[2] *= nw[s].z, o[3] *= nw[s].w;
+      T* dst = static_cast<T*>(p.out[s]) + t * W + c;
+      if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+      } else {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+      }
+    }
+  }
+  if (st != nullptr) {
+#pragma unroll
+    for (int j = 0; j + 1 < KEEP; ++j) *reinterpret_cast<float4*>(st + static_cast<long long>(j) * W + c) = win[j + 1];
+    *reinterpret_cast<float4*>(st + static_cast<long long>(KEEP > 0 ? KEEP - 1 : 0) * W + c) = cur;
+  }
+}
+
 // Small portions (each at most kCanonChunk tokens: a decoding batch): one block per portion does the residual update, the
 // statistics, the sublayers' inputs and the slot's new rows in a single launch.  A thread owns the channels c, c + 256, ...
-// through all phases, so it only ever rereads what it wrote itself; the rows' statistics cross the block once.
+// through all phases, so it only ever rereads what it wrote itself; the rows' statistics cross the block once.  A portion of
+// one token whose row fits one pass of the block takes the register path above.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 residual_norm_canon_small_kernel(const void* __restrict__ a, int a32, long long lda, const void* __restrict__ f, int f32, long long ldf,
-                                 float* __restrict__ x, float eps, const CanonParams p) {
+                                 float* __restrict__ x, float eps, const CanonParams p, int vec_ok) {
   __shared__ float red[32];
   __shared__ float rr[kCanonChunk];
   const int* pr = p.portions + 4 * blockIdx.x;
   const int t0 = pr[0], n = min(pr[1], kCanonChunk), pos0 = pr[2], slot = pr[3];
   if (n <= 0) return;
   const int W = p.W, taps = p.taps, keep = taps - 1;
+  if (n == 1 && vec_ok && (W >> 2) <= static_cast<int>(blockDim.x)) {       // uniform over the block
+    switch (taps) {
+#define LLMCTL_CANON_ONE(N) case N: residual_norm_canon_one_token<T, N>(a, a32, lda, f, f32, ldf, x, eps, p, t0, pos0, slot, red); return;
+      LLMCTL_CANON_ONE(1) LLMCTL_CANON_ONE(2) LLMCTL_CANON_ONE(3) LLMCTL_CANON_ONE(4)
+      LLMCTL_CANON_ONE(5) LLMCTL_CANON_ONE(6) LLMCTL_CANON_ONE(7) LLMCTL_CANON_ONE(8)
+#undef LLMCTL_CANON_ONE
+    }
+  }
   for (int k = 0; k < n; ++k) {
     const long long t = t0 + k;
     float* row = x + t * W;
@@ -332,7 +410,11 @@ LLMCTL_API int llmctl_residual_norm_canon_small(const void* a, int a_is_fp32, lo
   LLMCTL_REQUIRE((S == 1 || S == 2) && taps >= 1 && taps <= kCanonMaxTaps && W > 0 && (taps == 1 || state != nullptr) && x != nullptr);
   if (nportions == 0) return 0;
   CanonParams p{x, nullptr, {norm_w0, norm_w1}, {conv_w0, conv_w1}, {out0, out1}, portions, nullptr, state, S, W, taps};
-  LLMCTL_DISPATCH_DTYPE(out_is_fp32, T, (residual_norm_canon_small_kernel<T><<<nportions, 256, 0, (cudaStream_t)stream>>>(
-                                            a, a_is_fp32, lda, f, f_is_fp32, ldf, x, eps, p)));
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out0) | reinterpret_cast<uintptr_t>(out1) |
+                         reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(norm_w0) | reinterpret_cast<uintptr_t>(norm_w1)) & 15) == 0;
+  const int vec_ok = (W % 4 == 0 && aligned) ? 1 : 0;
+  const int threads = vec_ok ? min(1024, max(128, ((W / 4 + 31) / 32) * 32)) : 256;
+  LLMCTL_DISPATCH_DTYPE(out_is_fp32, T, (residual_norm_canon_small_kernel<T><<<nportions, threads, 0, (cudaStream_t)stream>>>(
+                                            a, a_is_fp32, lda, f, f_is_fp32, ldf, x, eps, p, vec_ok)));
   LLMCTL_RETURN_LAST();
 }

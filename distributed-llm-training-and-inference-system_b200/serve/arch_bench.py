@@ -437,6 +437,10 @@ def _tupidra_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str,
         bytes_ = T * W * (2 + 2 + 4 + 4) + T * W * (4 + 2 + 2)
         res[f"residual_norm_canon_{name}"] = {"ms": (t1 + t2) * 1e3, "ms_residual": t1 * 1e3, "ms_norm_canon": t2 * 1e3,
                                               "gbs": bytes_ / (t1 + t2) / 1e9, "frac_of_hbm": bytes_ / (t1 + t2) / 1e9 / peaks["hbm_gbs"]}
+        if new == 1:        # the model's decode path: one launch for all of it
+            t3 = _time_flushed(lambda: C.residual_norm_canon(a, f, x, 1e-6, nw, cw, b.portions, b.seq_rows, cstate, bf, small=True))
+            res[f"residual_norm_canon_{name}"].update({"ms_three_launches": (t1 + t2) * 1e3, "ms": t3 * 1e3, "gbs": bytes_ / t3 / 1e9,
+                                                       "frac_of_hbm": bytes_ / t3 / 1e9 / peaks["hbm_gbs"]})
         f32, w1, b1 = torch.randn(T, W, device=dev), torch.ones(W, device=dev), torch.zeros(W, device=dev)
         t = _time_flushed(lambda: E.parallel_residual(a, f32, x, 0.5, 1e-5, bf, w1, b1, want_fp32=True))
         bytes_ = T * W * (2 + 4 + 4 + 4 + 2 + 4)
