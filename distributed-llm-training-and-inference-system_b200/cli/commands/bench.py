@@ -44,7 +44,7 @@ def kernels(
     if not any((attention, matmul, kv_cache, flash, rope, norm, optimizer)):
         attention = matmul = True                     # the reference's default set (bench.py:29-30)
     if not torch.cuda.is_available():
-        console.print("[yellow]No GPU: kernel benchmarks need a B200 (run under gpurun).[/yellow]")
+        console.print("[yellow]No GPU: kernel benchmarks need a B200.[/yellow]")
         return []
     from ...ops import functional as ops
     from ...ops import serving as sops

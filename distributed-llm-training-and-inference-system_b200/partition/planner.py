@@ -155,7 +155,7 @@ class HardwareNumbers:
     collective_latency_us: float = 12.0
     # Per transformer layer and micro-batch (forward + backward), on top of the FLOP time at the dense rate: kernel
     # launch / host dispatch, small-GEMM wave quantisation and — under TP+SP — the exposed part of the fused
-    # all-gather / reduce-scatter.  Fitted to this framework's B200 runs (round 2, `profiles/`): GPT-7B TP=8+SP 48.2 ms,
+    # all-gather / reduce-scatter.  Fitted to this framework's B200 runs (`profiles/`): GPT-7B TP=8+SP 48.2 ms,
     # GPT-13B TP4xPP2 489 ms (8 x 2x2048) and 632 ms (16 x 1x2048), gpt-1b TP=2+SP 21 ms  ->  ~1.0 ms;
     # GPT-7B DP 179 ms, gpt-1b DP 28 ms  ->  ~0.15 ms.
     layer_overhead_ms: float = 0.15

@@ -46,13 +46,13 @@ NAMISUN_SIZES: Dict[str, Dict[str, Any]] = {
 
 
 TUPIDRA_SIZES: Dict[str, Dict[str, Any]] = {
-    # 6 layers: scan, soft-capped window attention (window 512 + 4 kept tokens), latent attention, twice; the second latent
+    # 6 layers: scan, latent attention, soft-capped window attention (window 512 + 8 kept tokens), twice; the second latent
     # layer reads the first one's cache; a gated GELU feed-forward beside every mixer; input convolutions of 4 taps
-    "w1024": dict(width=1024, vocab=32000, pattern="MALMAc", ff="1", taps=4, heads=8, kv_heads=2, dim=128, vdim=128, softcap=30.0,
-                  window=512, keep_first=4, lat_heads=8, lat_dim=128, rot_dim=64, lat_vdim=128, kv_rank=512, q_rank=384, inner=2048,
+    "w1024": dict(width=1024, vocab=32000, pattern="MLAMcA", ff="1", taps=4, heads=8, kv_heads=2, dim=128, vdim=128, softcap=30.0,
+                  window=512, keep_first=8, lat_heads=8, lat_dim=128, rot_dim=64, lat_vdim=128, kv_rank=512, q_rank=384, inner=2048,
                   state=16, dt_rank=64, conv=4, ff_size=4096),
-    "w2048": dict(width=2048, vocab=32000, pattern="MALMAc", ff="1", taps=4, heads=16, kv_heads=4, dim=128, vdim=128, softcap=30.0,
-                  window=512, keep_first=4, lat_heads=16, lat_dim=128, rot_dim=64, lat_vdim=128, kv_rank=512, q_rank=768, inner=4096,
+    "w2048": dict(width=2048, vocab=32000, pattern="MLAMcA", ff="1", taps=4, heads=16, kv_heads=4, dim=128, vdim=128, softcap=30.0,
+                  window=512, keep_first=8, lat_heads=16, lat_dim=128, rot_dim=64, lat_vdim=128, kv_rank=512, q_rank=768, inner=4096,
                   state=16, dt_rank=128, conv=4, ff_size=8192),
 }
 

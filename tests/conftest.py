@@ -10,7 +10,7 @@ if str(ROOT) not in sys.path:
 
 
 def pytest_configure(config):
-    config.addinivalue_line("markers", "gpu: needs a real B200 (run with `pytest -m gpu` under gpurun)")
+    config.addinivalue_line("markers", "gpu: needs a real B200 (run with `pytest -m gpu`)")
     config.addinivalue_line("markers", "slow: multi-process / long-running CPU test")
 
 
