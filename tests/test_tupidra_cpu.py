@@ -283,6 +283,30 @@ def test_portions_against_whole_prompt(name, cuts):
     assert torch.allclose(got, want, atol=F32 * max(1.0, float(want.abs().max())))
 
 
+def test_layers_of_one_kind_with_unlike_sizes_and_shared_caches_out_of_order():
+    """Two latent layers with caches of their own, two attention layers and two scans, each pair with its own sizes and
+    constants; the last two layers read the FIRST and the SECOND latent layer's cache (not the latest one), with their own
+    scale and the rotation base of the layer they read.  Portions cut anywhere against the whole-prompt oracle."""
+    a = small_cfg(pattern="LLAMcc", ff="111111", taps=3)
+    b = small_cfg(pattern="LLAMcc", ff="101101", heads=6, kv_heads=3, dim=4, vdim=6, softcap=3.0, window=5, keep_first=0, inner=24, state=3,
+                  dt_rank=5, conv=2, ff_size=24, lat_heads=2, lat_dim=4, rot_dim=6, lat_vdim=8, kv_rank=10, q_rank=7)
+    cfg = copy.deepcopy(a)
+    cfg["layers"][1], cfg["layers"][5] = copy.deepcopy(b["layers"][1]), copy.deepcopy(b["layers"][5])
+    cfg["layers"][4]["mixer"]["kv_from"], cfg["layers"][5]["mixer"]["kv_from"] = 0, 1
+    cfg["layers"].insert(3, copy.deepcopy(b["layers"][2]))
+    cfg["layers"].insert(5, copy.deepcopy(b["layers"][3]))            # L L A A' M M' c(0) c'(1)
+    for i in (1, 7):
+        cfg["layers"][i]["mixer"]["rot"]["base"] = 500.0
+    cfg["layers"][7]["mixer"]["scale"], cfg["layers"][3]["mixer"]["scale"], cfg["norm"]["eps"] = 0.7, 0.9, 1e-3
+    w = oracle.random_weights(cfg, 3)
+    torch.manual_seed(8)
+    cuts = [7, 2, 20, 1, 1, 3, 16]
+    toks = torch.randint(0, cfg["vocab"], (sum(cuts),)).tolist()
+    want = ref_logits(cfg, w, toks)
+    got = run_cut(make_engine(cfg, w), 1, toks, cuts)
+    assert torch.allclose(got, want, atol=F32 * max(1.0, float(want.abs().max())))
+
+
 def test_unequal_batches_skipped_steps_and_reused_pages_and_slots():
     """Three requests at a time in a pool of 2 state slots' worth ... no: 3 seats, 9 pages of 8 tokens: five requests of
     unequal length, portions of 1-11 tokens beside single tokens, requests that skip steps; pages and slots of finished
