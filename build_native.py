@@ -9,7 +9,7 @@ source or a header is newer than the object, so incremental rebuilds take second
 builds only what inference needs (GEMMs, norms, rotations, activations, attention over the paged caches,
 mixture-of-experts, sampling), ``serve-<design>`` only what replaying one design needs; entry points of the parts
 left out are simply absent from the library (``ops.native.has_symbol``), and a later build adds them.  The reference
-has no build system at all (SURVEY.md §2.3) — nothing to mirror here.
+has no build system at all — nothing to mirror here.
 """
 from __future__ import annotations
 

@@ -9,7 +9,7 @@
 // "inputs are ready" exchange and ends with an "I am done reading/writing" exchange, so buffers may be
 // reused immediately after the kernel by stream-ordered work on any rank.
 //
-// Reference: none — the reference contains no collective call at all (SURVEY.md §2.5); its "communication
+// Reference: none — the reference contains no collective call at all; its "communication
 // tuner" multiplies 1 ms by random noise (reference llmctl/plugins/autotuning.py:222-245).
 #include "symm.cuh"
 #include "../common/util.cuh"

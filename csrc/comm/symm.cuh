@@ -8,7 +8,7 @@
 //   consumer:  spin ld.acquire.sys flag >= epoch  ->  (fence.proxy.async if the data is then read by TMA)
 // The host passes a fresh, monotonically increasing `epoch` to every launch that uses a given pad slot.
 //
-// Reference: `llmctl.comms` is an empty package (reference llmctl/comms/__init__.py); SURVEY.md §5.8.
+// Reference: `llmctl.comms` is an empty package (reference llmctl/comms/__init__.py).
 #pragma once
 #include "../common/ptx.cuh"
 

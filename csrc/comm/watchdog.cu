@@ -2,7 +2,7 @@
 // flags registers a reader here; `llmctl_comm_watchdog_poll` gathers their records so one call tells the host
 // whether any wait on this device gave up, and on what.
 //
-// Reference: the reference has no collective code and no hang detection (SURVEY.md §5.2/§5.3).
+// Reference: the reference has no collective code and no hang detection.
 #include <cstdio>
 #include <cstring>
 #include <mutex>

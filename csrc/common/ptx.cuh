@@ -2,8 +2,8 @@
 // commit / ld / fences), cluster helpers, and the system-scope flag / multimem primitives used by the
 // fused compute+collective kernels.  Everything here is header-only and has no host-side state.
 //
-// Reference parity: the reference has no native code at all (SURVEY.md §2.3); these wrappers are the
-// substrate for kernels K0-K15 of SURVEY.md §2.6.b.
+// Reference parity: the reference has no native code at all; these wrappers are the
+// substrate for kernels K0-K15.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>

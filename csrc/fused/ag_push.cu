@@ -13,7 +13,7 @@
 // which waited for every peer's push n-1, which those peers issued after their GEMM n-2 — so nobody still reads the
 // buffer that call n overwrites.
 //
-// Reference: none (SP is a preset flag only: reference configs/presets/llama-7b-a100x8.toml:36).  SURVEY.md §2.6.b K1.
+// Reference: none (SP is a preset flag only: reference configs/presets/llama-7b-a100x8.toml:36).
 #include "../comm/symm.cuh"
 #include "../common/util.cuh"
 

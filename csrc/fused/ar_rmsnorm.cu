@@ -8,7 +8,7 @@
 // 64 of these run per generated token for a 32-layer model (two per layer).
 //
 // Reference: NCCL all-reduce + ATen add + rms_norm (three launches and a ~10 us collective); the reference
-// itself has no tensor parallelism at all (SURVEY.md §2.4 TP row; §2.6.b K11).
+// itself has no tensor parallelism at all.
 #include "../comm/symm.cuh"
 #include "../common/util.cuh"
 

@@ -20,7 +20,7 @@
 // Cross-GPU ordering uses epoch-numbered flags in the symmetric signal pads (csrc/comm/symm.cuh).
 //
 // Reference: NCCL all-reduce inside DDP + torch.optim.AdamW + clip_grad_norm_
-// (reference llmctl/runtime/engine.py:265-267,289,295-303).  SURVEY.md §2.6.b K7.
+// (reference llmctl/runtime/engine.py:265-267,289,295-303).
 #include "../comm/symm.cuh"
 #include "../common/util.cuh"
 

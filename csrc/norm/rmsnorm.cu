@@ -1,8 +1,8 @@
 // K3: RMSNorm / LayerNorm forward + backward for bf16 activations with fp32 statistics, with the
 // residual add fused into the forward and the residual-gradient add fused into the backward.
 //
-// The reference has no norm kernel: HF modules call ATen (SURVEY.md §2.6.a "Train fwd+loss",
-// reference llmctl/runtime/engine.py:284).  Baseline to beat: ATen rms_norm / layer_norm.
+// The reference has no norm kernel: HF modules call ATen
+// (reference llmctl/runtime/engine.py:284).  Baseline to beat: ATen rms_norm / layer_norm.
 //
 // Forward : one warp per row, the whole row lives in registers (<= 32 x 16 B per lane), one pass over
 //           HBM.  h = x (+ residual) ; y = h * rsqrt(mean(h^2)+eps) * w.

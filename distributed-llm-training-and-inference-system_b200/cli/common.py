@@ -3,7 +3,7 @@
 
 Reference: the short forms are advertised (reference README.md:39-54) but broken — the group callbacks
 call the command with no arguments so typer ``OptionInfo`` objects arrive as values
-(reference llmctl/cli/commands/init.py:270-271, train.py:112-113; SURVEY.md §2.7).
+(reference llmctl/cli/commands/init.py:270-271, train.py:112-113).
 """
 from __future__ import annotations
 

@@ -8,7 +8,7 @@ buffers ``stage[world, M/world, N]`` for K2, the signal pads and the per-call ep
 fused linears in ``parallel/tp.py``; anything unsupported falls back to the NCCL collectives there
 (baseline path, also the CPU/gloo path).
 
-Reference: ``llmctl.comms`` is an empty package (reference llmctl/comms/__init__.py; SURVEY.md §2.2 E1).
+Reference: ``llmctl.comms`` is an empty package (reference llmctl/comms/__init__.py).
 """
 from __future__ import annotations
 

@@ -2,11 +2,10 @@
 
 Rank layout: ``rank = pp_rank * (dp * tp) + dp_rank * tp + tp_rank`` — TP is innermost so a TP group is a
 set of adjacent GPUs, DP next, PP outermost (only PP traffic would ever leave an NVSwitch domain).
-A ``cp`` axis name is reserved (size 1) so context parallelism can be added without renumbering
-(SURVEY.md §5.7).
+A ``cp`` axis name is reserved (size 1) so context parallelism can be added without renumbering.
 
 Reference: no mesh exists in the reference — TP/PP/ZeRO are integers in a plan file that nothing reads
-(reference llmctl/cli/commands/plan.py:176-186, SURVEY.md §0 item 2); process-group creation is delegated
+(reference llmctl/cli/commands/plan.py:176-186); process-group creation is delegated
 to accelerate (reference llmctl/runtime/engine.py:105-110).  Rendezvous env handling replaces
 reference llmctl/runtime/launcher.py:73-79.
 """

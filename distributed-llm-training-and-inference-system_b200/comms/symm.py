@@ -4,14 +4,14 @@
 rank's address space (CUDA VMM + fabric/FD handle exchange), giving each rank the table of peer base pointers
 that the fused kernels (K1 ag_gemm, K2 gemm_rs, K7 rs_adam, K11 ar_rmsnorm) dereference directly with P2P
 loads / stores / reductions, plus an optional NVLS multicast address.  The allocation + rendezvous plumbing is
-``torch.distributed._symmetric_memory`` (framework layer, allowed by SURVEY.md §5.8 item 1); everything that
+``torch.distributed._symmetric_memory`` (framework layer); everything that
 moves data is our own kernels.
 
 Signal pads: each buffer carries a small int32 pad per rank; slots are assigned by name through
 ``SignalSlots`` and every use passes a monotonically increasing epoch (flags are never reset).
 
 Reference: ``llmctl.comms`` is an empty package (reference llmctl/comms/__init__.py); the reference's only
-collectives are the implicit DDP all-reduces inside accelerate (SURVEY.md §2.5).
+collectives are the implicit DDP all-reduces inside accelerate.
 """
 from __future__ import annotations
 

@@ -1,4 +1,4 @@
-"""Validated schemas for every file format of SURVEY.md §2.8 (pydantic v2).
+"""Validated schemas for every file format (pydantic v2).
 
 The reference has no validation at all — ``llmctl.config`` is an empty package and configs are raw dicts
 (reference llmctl/config/__init__.py; reference llmctl/cli/commands/plan.py:224-237).  These models accept
@@ -7,7 +7,7 @@ files keep working) and add the new keys this framework executes (sequence_paral
 activation_checkpoint, ...).
 
 Precedence implemented by ``resolve_training_config``:
-    defaults < preset TOML (--config) < plan TOML (--plan) < explicit CLI flags        
+    defaults < preset TOML (--config) < plan TOML (--plan) < explicit CLI flags       
 """
 from __future__ import annotations
 

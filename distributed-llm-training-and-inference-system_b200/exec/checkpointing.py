@@ -8,8 +8,7 @@
 * ``none``      — store everything.
 
 Reference: ``activation_checkpoint = "selective"`` is a config string with no consumer
-(reference configs/presets/llama-7b-a100x8.toml:38, reference llmctl/cli/commands/init.py:138;
-SURVEY.md §2.4 last rows).
+(reference configs/presets/llama-7b-a100x8.toml:38, reference llmctl/cli/commands/init.py:138).
 """
 from __future__ import annotations
 

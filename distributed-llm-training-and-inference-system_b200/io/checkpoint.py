@@ -1,6 +1,6 @@
 """Checkpoint save / resume / GC.
 
-Layout (keeps the reference's names, SURVEY.md §2.8 "Checkpoint layout", reference
+Layout (keeps the reference's names, reference
 llmctl/runtime/engine.py:363-394):
 
     <output_dir>/checkpoint-<step>/            (and <output_dir>/final/)

@@ -9,7 +9,7 @@
   asynchronous H2D copy on a side stream (double buffered).
 
 Reference: the reference's "dataset" is three hard-coded sentences x100 tokenised to 512 tokens
-(reference llmctl/runtime/engine.py:142-204); ``llmctl.io`` is an empty package (SURVEY.md §2.2 E4).
+(reference llmctl/runtime/engine.py:142-204); ``llmctl.io`` is an empty package.
 """
 from __future__ import annotations
 
@@ -86,7 +86,7 @@ class TokenLoader:
     """Yields ``(tokens[B,S], targets[B,S])`` on ``device`` for this DP rank.
 
     Global batch ``g`` consumes samples ``[cursor, cursor + micro_batch * dp)``; rank ``r`` takes the r-th
-    slice.  ``state_dict``/``load_state_dict`` make the stream resumable (SURVEY.md §5.4)."""
+    slice.  ``state_dict``/``load_state_dict`` make the stream resumable."""
 
     def __init__(self, dataset, micro_batch: int, dp_rank: int = 0, dp_size: int = 1, device=None,
                  shuffle_seed: Optional[int] = None, prefetch: bool = True):

@@ -4,9 +4,9 @@ report consumed by ``llmctl health drift``.
 Public names and thresholds follow reference llmctl/metrics/health.py (system: cpu 80/95 %, memory 85/95 %,
 disk 85/95 %, GPU memory 90/98 %; training: stall > 300 s, non-finite loss, grad norm outside (0.001, 100);
 inference: error rate > 5 %, average latency > 10 s, queue > 100).  Differences: the disk and GPU-memory
-thresholds actually fire (the reference stores those metrics under one name and looks them up under another,
-SURVEY.md §2.10 D12), shared state is lock-protected, and the monitors are fed by the train loop and the
-server (the reference never calls them, SURVEY.md §5.3).
+thresholds actually fire (the reference stores those metrics under one name and looks them up under another),
+shared state is lock-protected, and the monitors are fed by the train loop and the
+server (the reference never calls them).
 """
 from __future__ import annotations
 

@@ -1,5 +1,5 @@
-"""Glue between the train loop / server and the metrics subsystem (the reference never wires them:
-SURVEY.md §5.5 "No caller outside metrics/").  Kept tiny so the hot loop pays one host sync per logging
+"""Glue between the train loop / server and the metrics subsystem (the reference never wires
+them).  Kept tiny so the hot loop pays one host sync per logging
 window only."""
 from __future__ import annotations
 

@@ -8,7 +8,7 @@ Metric names are the reference's (reference llmctl/metrics/observability.py:237-
 ``llmctl_system_memory_percent``, ``llmctl_system_gpu_memory_used_gb{gpu_id}``; added:
 ``llmctl_training_grad_norm``, ``llmctl_training_mfu``, ``llmctl_training_step_seconds``,
 ``llmctl_inference_ttft_seconds``, ``llmctl_system_gpu_utilization{gpu_id}`` (real NVML value — the
-reference hard-codes 0.0, SURVEY.md §2.10 D15).  Counters and the histogram are actually updated.
+reference hard-codes 0.0).  Counters and the histogram are actually updated.
 Exporters start only when asked (``setup_observability(prometheus_port=..., otlp_endpoint=...)``).
 """
 from __future__ import annotations

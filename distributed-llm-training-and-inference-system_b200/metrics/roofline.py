@@ -6,7 +6,7 @@ cuBLAS bf16 throughput on this pool's B200s); the fallback numbers are the ones 
 measured peer copy (900 nominal).
 
 Reference: the telemetry metric names ``flops, mem_bw, comm_bw`` are declared and never computed
-(reference llmctl/cli/commands/init.py:155, SURVEY.md §2.2 E12).
+(reference llmctl/cli/commands/init.py:155).
 """
 from __future__ import annotations
 

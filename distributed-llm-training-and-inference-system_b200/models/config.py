@@ -1,4 +1,4 @@
-"""Model definition schema (the reference's model JSON, SURVEY.md §2.8) and built-in presets.
+"""Model definition schema (the reference's model JSON) and built-in presets.
 
 Reference: reference configs/models/llama-7b.json:1-24 and the templates in reference
 llmctl/cli/commands/init.py:16-51 (gpt-7b, gpt-13b, llama-7b).  ``gpt-125m`` is added because
@@ -52,7 +52,7 @@ class ModelConfig:
         return self.activation in ("silu", "swiglu")
 
     def num_parameters(self) -> int:
-        """Exact parameter count of the model this framework builds (fixes SURVEY.md §2.10 D10)."""
+        """Exact parameter count of the model this framework builds."""
         h, f, L, v = self.hidden, self.ffn, self.layers, self.vocab_size
         attn = 4 * h * (self.heads * self.head_dim)
         mlp = (3 if self.gated else 2) * h * f

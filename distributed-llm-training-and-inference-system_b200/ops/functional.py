@@ -6,7 +6,7 @@ Every op has two implementations selected at call time:
   path; it raises if the library is missing rather than silently falling back.
 * **baseline** — plain PyTorch library ops (cuBLAS / SDPA / ATen).  Used on CPU (gloo plumbing tests),
   for non-bf16 dtypes, and on GPU only when explicitly requested with ``set_backend("baseline")`` — this
-  is the "B-lib" baseline of BASELINE.md §2 (what the reference's HF model would execute,
+  is the "B-lib" baseline (what the reference's HF model would execute,
   reference llmctl/runtime/engine.py:284).
 
 Each sub-system can be switched independently (``KernelConfig``) so the auto-tuner and the benchmarks

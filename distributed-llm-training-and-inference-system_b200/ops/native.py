@@ -5,7 +5,7 @@ pointers plus the current CUDA stream.  Loading is lazy.  On a machine with a GP
 present — ``lib()`` raises instead of letting callers fall back silently (the round-end driver records
 which ``.so`` files were actually loaded).
 
-Reference parity: the reference has no native layer (SURVEY.md §2.3).
+Reference parity: the reference has no native layer.
 """
 from __future__ import annotations
 

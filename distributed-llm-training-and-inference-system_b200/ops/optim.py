@@ -2,8 +2,8 @@
 
 Reference: ``torch.optim.AdamW(lr, betas=(0.9, 0.95), eps=1e-8, weight_decay)`` at reference
 llmctl/runtime/engine.py:230-235 and ``accelerator.clip_grad_norm_`` at engine.py:295-299.  Differences by
-design: fp32 master weights + moments (the reference steps fp16 weights directly, SURVEY.md §2.10 D8), the
-clip coefficient stays on the device, and a non-finite gradient norm skips the step (SURVEY.md §5.3).
+design: fp32 master weights + moments (the reference steps fp16 weights directly), the
+clip coefficient stays on the device, and a non-finite gradient norm skips the step.
 """
 from __future__ import annotations
 

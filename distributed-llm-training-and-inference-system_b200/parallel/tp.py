@@ -2,8 +2,8 @@
 
 * ``ColumnParallelLinear`` / ``RowParallelLinear`` — weights sharded over the TP group.
 * With ``sequence_parallel`` the activations outside attention/MLP are sharded on the token dim:
-  all-gather before the column-parallel GEMM and reduce-scatter after the row-parallel GEMM
-  (SURVEY.md §5.7a).  On CUDA these two pairs are the fused K1 ``ag_gemm`` / K2 ``gemm_rs`` kernels
+  all-gather before the column-parallel GEMM and reduce-scatter after the row-parallel GEMM.
+  On CUDA these two pairs are the fused K1 ``ag_gemm`` / K2 ``gemm_rs`` kernels
   (``comms/fused.py``); the NCCL/gloo collectives below are the baseline path and the CPU path.
 * ``VocabParallelEmbedding`` and ``vocab_parallel_cross_entropy`` (K15).
 

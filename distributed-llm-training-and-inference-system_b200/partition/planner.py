@@ -2,12 +2,12 @@
 against *measured* hardware numbers and pick the fastest plan that fits in memory.
 
 Reference: ``ParallelismPlanner`` lives inside the CLI file reference llmctl/cli/commands/plan.py:18-202
-(``llmctl.partition`` itself is an empty package).  Its estimators have unit and counting defects
-(SURVEY.md §2.10 D10, D11): parameters ignore the third SwiGLU matrix and the LM head, "communication" in
+(``llmctl.partition`` itself is an empty package).  Its estimators have unit and counting defects:
+parameters ignore the third SwiGLU matrix and the LM head, "communication" in
 GB is compared with GB/s, ZeRO-1 has no memory effect, DP never enters the memory model and the score
 always prefers maximal TP.  ``ReferenceCostModel`` re-states those formulas only so that
-``--cost-model reference`` reproduces the reference's outputs bit-for-bit for users who depend on them
-(golden values in SURVEY.md §3.3); ``MeasuredCostModel`` is the real planner.
+``--cost-model reference`` reproduces the reference's outputs bit-for-bit for users who depend on them (the CLI tests hold
+golden values); ``MeasuredCostModel`` is the real planner.
 """
 from __future__ import annotations
 
@@ -134,7 +134,7 @@ class ReferenceCostModel:
     def manual(self, tp: Optional[int], pp: Optional[int], zero: Optional[int]) -> Plan:
         gpus = self.hw.get("gpu", {}).get("count", 1)
         tp, pp = tp or 1, pp or 1
-        zero = 1 if zero is None else zero      # an explicit 0 stays 0 (fixes SURVEY.md §2.10 D9)
+        zero = 1 if zero is None else zero      # an explicit 0 stays 0
         dp = max(gpus // (tp * pp), 1)
         return Plan(tp, pp, dp, zero, 1, dp * 4, self.memory_gb(tp, pp, zero, 1), self.comm(tp, pp, zero, dp * 4, 1),
                     self.flops(dp * 4, self.SEQ), gradient_accumulation_steps=4)
@@ -328,7 +328,7 @@ class MeasuredCostModel:
     def search(self, max_memory_gb: Optional[float] = None, global_batch: Optional[int] = None,
                pins: Optional[Dict[str, Any]] = None, top_k: int = 8) -> List[Plan]:
         """Feasible plans ranked by tokens/s (descending).  ``pins`` fixes any subset of the axes — partial pins
-        in auto mode are allowed (``--strategy auto --pipeline-parallel 2``; SURVEY.md §7.4 item 9)."""
+        in auto mode are allowed (``--strategy auto --pipeline-parallel 2``)."""
         cap = max_memory_gb if max_memory_gb else self.hw.memory_gb * 0.92
         plans = [p for p in self.candidates(global_batch, pins or {}) if p.estimated_memory_gb <= cap]
         plans.sort(key=lambda p: (-p.estimated_tokens_per_s, p.estimated_memory_gb))

@@ -4,7 +4,7 @@ cache — the API of reference llmctl/plugins/autotuning.py (``TuningConfig``, `
 ``create_auto_tuner``; cache keys ``matmul_{(m,k,n)}_{device}``, ``attention_{seq}_{hd}_{device}``,
 ``comm_{shape}_{dtype}``).
 
-What differs (SURVEY.md §2.10 D13, §2.5 "Communication tuner"): the knobs are real.  On a GPU the matmul
+What differs: the knobs are real.  On a GPU the matmul
 tuner drives the tcgen05 GEMM's tile shape / CTA-pair mode / SM budget, the attention tuner switches between
 the attention back-ends, and the communication tuner *measures* an all-reduce over the live process group
 for each bucket size (the reference "measures" ``1 ms x random noise``).  ``warmup_iterations``,

@@ -6,7 +6,7 @@ TP-sharded) model, the ZeRO optimizer, the token loader, the 1F1B schedule, chec
 Public surface kept from the reference (reference llmctl/runtime/engine.py:30-70,72-411):
 ``TrainingConfig`` with the same field names, ``TrainingEngine.load_model_and_tokenizer / prepare_datasets /
 setup_optimizer_and_scheduler / train / evaluate / save_checkpoint / load_checkpoint`` and
-``create_training_config``.  What differs, on purpose (SURVEY.md §2.10): the plan (TP/PP/SP/ZeRO) is
+``create_training_config``.  What differs, on purpose: the plan (TP/PP/SP/ZeRO) is
 executed rather than ignored; seeds are applied (D7); logging / eval / checkpoint cadence is per optimizer
 step (D6); resume restores everything (D5); CPU runs checkpoint and synchronise gradients (D4); master
 weights are fp32 (D8); the loss is never ``.item()``-ed inside the hot loop.
@@ -112,7 +112,7 @@ def create_training_config(**kwargs) -> TrainingConfig:
 
 def apply_plan(cfg: TrainingConfig, plan: Dict[str, Any]) -> TrainingConfig:
     """Fold a plan TOML's ``[parallelism]`` table into the config (the reference stores the plan path and
-    never reads it: reference llmctl/runtime/launcher.py:34, SURVEY.md §0 item 2)."""
+    never reads it: reference llmctl/runtime/launcher.py:34)."""
     par = plan.get("parallelism", plan)
     cfg.tensor_parallel = int(par.get("tensor_parallel", cfg.tensor_parallel))
     cfg.pipeline_parallel = int(par.get("pipeline_parallel", cfg.pipeline_parallel))

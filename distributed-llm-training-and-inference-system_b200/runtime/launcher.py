@@ -2,7 +2,7 @@
 
 Surface of reference llmctl/runtime/launcher.py:21-332 (``LaunchConfig``, ``BaseLauncher``,
 ``LocalLauncher``, ``SlurmLauncher``, ``MPILauncher``, ``create_launcher``, ``ProcessOrchestrator``).
-Fixed on purpose (SURVEY.md §2.10 D14): ``sys.executable`` instead of ``python``, a free rendezvous port
+Fixed on purpose: ``sys.executable`` instead of ``python``, a free rendezvous port
 bound to 127.0.0.1 instead of a hard-coded 29500/localhost, no forced ``CUDA_VISIBLE_DEVICES``, elastic
 restarts (``--max-restarts``) with auto-resume, ``k8s`` fails with a clear message (E7), MPI ranks come
 from the real OMPI environment instead of a constant 0.

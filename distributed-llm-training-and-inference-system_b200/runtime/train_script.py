@@ -2,7 +2,7 @@
 
 Same flags as reference llmctl/runtime/train_script.py:18-89 plus the plan-execution flags.  Precedence is
 ``defaults < --config file (JSON with TrainingConfig keys, or the TOML preset) < --plan < flags actually
-passed`` — the reference lets CLI *defaults* clobber the file (train_script.py:100-131; SURVEY.md §5.6).
+passed`` — the reference lets CLI *defaults* clobber the file (train_script.py:100-131).
 """
 from __future__ import annotations
 

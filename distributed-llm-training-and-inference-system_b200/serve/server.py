@@ -1,6 +1,6 @@
 """HTTP inference server (FastAPI + uvicorn): ``POST /v1/completions``, ``GET /v1/models``, ``GET /health``,
 ``GET /metrics`` — the API of reference llmctl/serve/server.py:253-407 (same request / response models,
-503 "Server at capacity", CORS ``*``) with the defects fixed (SURVEY.md §2.10): generation runs to EOS or
+503 "Server at capacity", CORS ``*``) with the defects fixed: generation runs to EOS or
 ``max_tokens`` instead of stopping after one token (D1); there is no padding, so no sampling from pad
 positions (D2); the engine loop runs on its own thread so a forward never blocks the event loop (D3);
 ``stream=true`` streams server-sent events instead of being ignored.

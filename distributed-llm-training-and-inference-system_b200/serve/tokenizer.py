@@ -1,7 +1,7 @@
 """Tokenizers for serving / eval without network access.
 
 ``ByteTokenizer`` is a dependency-free byte-level tokenizer (ids 0..255 = bytes, then specials) so that
-``/v1/completions`` works on random-init checkpoints with no hub files (SURVEY.md §9 item 3).  When the
+``/v1/completions`` works on random-init checkpoints with no hub files.  When the
 artifact directory contains HF tokenizer files they are used instead (reference
 llmctl/serve/server.py:146-170 loads ``AutoTokenizer.from_pretrained``).
 """

@@ -2,7 +2,7 @@
 the engine's own phase names.  ``LLMCTL_NVTX=0`` disables them, ``LLMCTL_NVTX=kernels`` additionally wraps each
 C-ABI kernel call (see ``ops/native.py``).  Off the GPU everything is a no-op.
 
-Reference: no profiler hooks exist anywhere in the reference (SURVEY.md §5.1; the preset's ``profiling`` table in
+Reference: no profiler hooks exist anywhere in the reference (the preset's ``profiling`` table in
 reference configs/presets/llama-7b-a100x8.toml:69-73 has no consumer).
 """
 from __future__ import annotations

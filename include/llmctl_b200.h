@@ -1,4 +1,4 @@
-/* C ABI of libllmctl_b200.so — hand-written sm_100a kernels (SURVEY.md §2.6.b, K0..K15).
+/* C ABI of libllmctl_b200.so — hand-written sm_100a kernels.
  *
  * Conventions
  *   - every function returns a cudaError_t value as int (0 = success, 1 = invalid argument);
@@ -6,7 +6,7 @@
  *   - nothing here allocates device memory: outputs and scratch are passed in by the caller;
  *   - launches are asynchronous on `stream`.
  *
- * The reference repository ships no native code (SURVEY.md §2.3); the "Reference:" notes name the
+ * The reference repository ships no native code; the "Reference:" notes name the
  * library path the reference reaches for the same work.
  */
 #ifndef LLMCTL_B200_H_

@@ -71,7 +71,7 @@ def test_plan_workflow(tmp_path):
 
 
 def test_plan_reference_golden(tmp_path):
-    """`--cost-model reference` reproduces the reference planner's numbers (SURVEY.md §3.3 golden values)."""
+    """`--cost-model reference` reproduces the reference planner's numbers (golden values)."""
     model = tmp_path / "llama-7b.json"
     model.write_text(json.dumps({"name": "llama-7b", "layers": 32, "hidden": 4096, "ffn": 11008, "heads": 32, "vocab_size": 32000}))
     hw = tmp_path / "a100x8.json"
@@ -147,7 +147,8 @@ def test_health_and_tune(tmp_path):
     rep = tmp_path / "h.json"
     r = run("health", "check", "--component", "system", "--save-report", str(rep))
     assert r.returncode == 0 and json.loads(rep.read_text())["system"]["component"] == "system"
-    assert run("health", "drift", "--baseline-file", str(rep), "--tolerance", "1000").returncode == 0
+    # a wide tolerance: on a busy host cpu_usage can move from a fraction of a percent to 100 between the two calls
+    assert run("health", "drift", "--baseline-file", str(rep), "--tolerance", "1e9").returncode == 0
     bad = json.loads(rep.read_text()); bad["system"]["metrics"]["memory_usage"] = 0.001
     (tmp_path / "bad.json").write_text(json.dumps(bad))
     assert run("health", "drift", "--baseline-file", str(tmp_path / "bad.json"), "--tolerance", "10").returncode == 1
@@ -169,7 +170,7 @@ def test_trace_visualize(tmp_path):
 
 
 def test_elastic_restart_after_injected_kill(tmp_path):
-    """Fault drill (SURVEY §5.3): rank 1 is killed at step 3 of a 2-process gloo run; torchrun restarts the group, the
+    """Fault drill: rank 1 is killed at step 3 of a 2-process gloo run; torchrun restarts the group, the
     workers resume from the newest complete checkpoint on their own and the run finishes all 6 steps."""
     out = tmp_path / "elastic"
     r = run("--seed", "3", "train", "launch", "--model", "gpt-tiny", "--output-dir", str(out), "--batch-size", "2", "--seq-len", "32",

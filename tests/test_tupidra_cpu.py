@@ -124,7 +124,7 @@ def test_gated_gelu_and_sigmoid_gate():
 
 
 @pytest.mark.parametrize("dims,base,scaling", [(8, 10000.0, {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}),
-                                               (32, 1e6, {"factor": 16.0, "original": 4096, "fast": 32.0, "slow": 1.0}),
+                                               (48, 5e5, {"factor": 16.0, "original": 4096, "fast": 24.0, "slow": 2.0}),
                                                (4, 100.0, {"factor": 2.0, "original": 16, "fast": 1.0, "slow": 1.0}),     # lo == hi: the ramp's floor
                                                (6, 50.0, None)])
 def test_rotation_spectrum(dims, base, scaling):

@@ -1,4 +1,4 @@
-"""Unit tests the reference never had (SURVEY.md §4): planner, config schemas, health thresholds, autotuner,
+"""Unit tests the reference never had: planner, config schemas, health thresholds, autotuner,
 plugin registry, checkpoint GC, LR schedule, export re-sharding, roofline."""
 import json
 import math

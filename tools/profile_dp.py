@@ -5,7 +5,7 @@ Two views, both from rank 0 (never a bench number):
   * phases  : CUDA-event times on the compute stream for forward / backward / optimizer.step of each step (the
               side-stream work of K7 shows up as waiting inside the phase that consumes it);
   * kernels : per-kernel device-time totals of two profiled steps (torch.profiler / CUPTI).
-    scripts/torchrun_local.sh 2 tools/profile_dp.py --zero-stage 1 --out gpurun_out/profile_dp2.json
+    scripts/torchrun_local.sh 2 tools/profile_dp.py --zero-stage 1 --out profile_dp2.json
 """
 import argparse
 import json
