@@ -42,6 +42,9 @@ NAMISUN_SIZES: Dict[str, Dict[str, Any]] = {
     "w2048": dict(width=2048, vocab=32000, pattern="MGAMGA", moe="1", loop=None, heads=16, kv_heads=4, dim=64, vdim=128, rot_dims=64,
                   rot_factor=8.0, gla_heads=16, gla_dim=64, gla_vdim=128, decay_rank=16, inner=4096, state=16, dt_rank=128, conv=4,
                   experts=6, identity=2, top=2, groups=(4, 2), ff=2048, limit=7.0),
+    "w4096": dict(width=4096, vocab=32000, pattern="MGAMGA", moe="1", loop=None, heads=32, kv_heads=8, dim=64, vdim=128, rot_dims=64,
+                  rot_factor=8.0, gla_heads=32, gla_dim=64, gla_vdim=128, decay_rank=16, inner=8192, state=16, dt_rank=256, conv=4,
+                  experts=6, identity=2, top=2, groups=(4, 2), ff=3072, limit=7.0),
 }
 
 
@@ -54,6 +57,9 @@ TUPIDRA_SIZES: Dict[str, Dict[str, Any]] = {
     "w2048": dict(width=2048, vocab=32000, pattern="MLAMcA", ff="1", taps=4, heads=16, kv_heads=4, dim=128, vdim=128, softcap=30.0,
                   window=512, keep_first=8, lat_heads=16, lat_dim=128, rot_dim=64, lat_vdim=128, kv_rank=512, q_rank=768, inner=4096,
                   state=16, dt_rank=128, conv=4, ff_size=8192),
+    "w4096": dict(width=4096, vocab=32000, pattern="MLAMcA", ff="1", taps=4, heads=32, kv_heads=8, dim=128, vdim=128, softcap=30.0,
+                  window=512, keep_first=8, lat_heads=32, lat_dim=128, rot_dim=64, lat_vdim=128, kv_rank=512, q_rank=1536, inner=8192,
+                  state=16, dt_rank=256, conv=4, ff_size=16384),
 }
 
 
