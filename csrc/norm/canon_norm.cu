@@ -47,6 +47,40 @@ residual_rms_kernel(const void* __restrict__ a, int a32, long long lda, const vo
   if (threadIdx.x == 0) r[t] = 1.f / sqrtf(ss / static_cast<float>(W) + eps);
 }
 
+// four neighbouring elements of a bf16 or fp32 row (the address a multiple of 8 or 16 bytes)
+__device__ __forceinline__ float4 load4_any(const void* p, int is32, long long i) {
+  if (is32) return *reinterpret_cast<const float4*>(static_cast<const float*>(p) + i);
+  const uint2 u = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p) + i);
+  return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                     __uint_as_float(u.y & 0xffff0000u));
+}
+
+// The same with 16-byte accesses (W and the strides multiples of 4, aligned rows): a thread owns four neighbouring columns.
+__global__ void __launch_bounds__(256)
+residual_rms_vec_kernel(const void* __restrict__ a, int a32, long long lda, const void* __restrict__ f, int f32, long long ldf,
+                        float* __restrict__ x, float* __restrict__ r, int W, float eps) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  float* row = x + t * W;
+  float ss = 0.f;
+  for (int c = threadIdx.x << 2; c < W; c += blockDim.x << 2) {
+    float4 v = *reinterpret_cast<const float4*>(row + c);
+    if (a != nullptr || f != nullptr) {
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (a != nullptr) s = load4_any(a, a32, t * lda + c);
+      if (f != nullptr) {
+        const float4 g = load4_any(f, f32, t * ldf + c);
+        s.x += g.x, s.y += g.y, s.z += g.z, s.w += g.w;
+      }
+      v.x += s.x, v.y += s.y, v.z += s.z, v.w += s.w;
+      *reinterpret_cast<float4*>(row + c) = v;
+    }
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = block_sum(ss, red);
+  if (threadIdx.x == 0) r[t] = 1.f / sqrtf(ss / static_cast<float>(W) + eps);
+}
+
 constexpr int kCanonMaxTaps = 8;
 constexpr int kCanonChunk = 8;      // most consecutive tokens a thread of the vector kernel walks
 
@@ -116,19 +150,31 @@ norm_canon_vec_kernel(const CanonParams p, int tokens, int tokens_per_cta) {
   constexpr int KEEP = TAPS - 1;
   const int W = p.W, W4 = W >> 2;
   const int t_begin = blockIdx.x * tokens_per_cta, t_end = min(tokens, t_begin + tokens_per_cta);
+  // what is the same for every thread of the block is looked up once: a token's statistics and its index within its
+  // portion (0: the window starts anew).  Per-thread scalar loads of these fill the load queue of the SM.
+  __shared__ float s_rr[kCanonChunk];
+  __shared__ int s_within[kCanonChunk];
+  if (threadIdx.x < kCanonChunk) {
+    const int t = t_begin + threadIdx.x;
+    s_rr[threadIdx.x] = t < t_end ? p.r[t] : 0.f;
+    s_within[threadIdx.x] = t < t_end ? t - p.portions[4 * p.seq_rows[t]] : -1;
+  }
+  __syncthreads();
   for (int c4 = blockIdx.y * blockDim.x + threadIdx.x; c4 < W4; c4 += gridDim.y * blockDim.x) {
     const int c = c4 << 2;
-    float cw[2][4][TAPS];
+    float cw[2][4 * TAPS];              // a channel's taps follow one another: [channel * TAPS + tap], 16 bytes at a time
     float4 nw[2];
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
       nw[s] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (s < p.S) {
         nw[s] = *reinterpret_cast<const float4*>(p.norm_w[s] + c);
+        const float4* src = reinterpret_cast<const float4*>(p.conv_w[s] + static_cast<long long>(c) * TAPS);
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-#pragma unroll
-          for (int j = 0; j < TAPS; ++j) cw[s][ch][j] = p.conv_w[s][static_cast<long long>(c + ch) * TAPS + j];
+        for (int j = 0; j < TAPS; ++j) {
+          const float4 v = src[j];
+          cw[s][4 * j] = v.x, cw[s][4 * j + 1] = v.y, cw[s][4 * j + 2] = v.z, cw[s][4 * j + 3] = v.w;
+        }
       }
     }
     // all rows of the chunk are requested before the first one is used
@@ -137,20 +183,17 @@ norm_canon_vec_kernel(const CanonParams p, int tokens, int tokens_per_cta) {
 #pragma unroll
     for (int k = 0; k < kCanonChunk; ++k) {
       rows[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-      rr[k] = 0.f;
-      if (t_begin + k < t_end) {
-        rows[k] = *reinterpret_cast<const float4*>(p.x + static_cast<long long>(t_begin + k) * W + c);
-        rr[k] = p.r[t_begin + k];
-      }
+      rr[k] = s_rr[k];
+      if (t_begin + k < t_end) rows[k] = *reinterpret_cast<const float4*>(p.x + static_cast<long long>(t_begin + k) * W + c);
     }
     float4 win[KEEP > 0 ? KEEP : 1];
 #pragma unroll
     for (int k = 0; k < kCanonChunk; ++k) {
       const int t = t_begin + k;
       if (t >= t_end) break;
-      const int* pr = p.portions + 4 * p.seq_rows[t];
-      const int i = t - pr[0];
+      const int i = s_within[k];
       if (k == 0 || i == 0) {
+        const int* pr = p.portions + 4 * p.seq_rows[t];
         const bool has_state = pr[2] > 0 && pr[3] >= 0;
 #pragma unroll
         for (int j = 0; j < KEEP; ++j) {
@@ -171,14 +214,14 @@ norm_canon_vec_kernel(const CanonParams p, int tokens, int tokens_per_cta) {
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
         if (s < p.S) {
-          float o[4] = {cur.x * (1.f + cw[s][0][KEEP]), cur.y * (1.f + cw[s][1][KEEP]), cur.z * (1.f + cw[s][2][KEEP]),
-                        cur.w * (1.f + cw[s][3][KEEP])};
+          float o[4] = {cur.x * (1.f + cw[s][KEEP]), cur.y * (1.f + cw[s][TAPS + KEEP]), cur.z * (1.f + cw[s][2 * TAPS + KEEP]),
+                        cur.w * (1.f + cw[s][3 * TAPS + KEEP])};
 #pragma unroll
           for (int j = 0; j < KEEP; ++j) {
-            o[0] += cw[s][0][j] * win[j].x;
-            o[1] += cw[s][1][j] * win[j].y;
-            o[2] += cw[s][2][j] * win[j].z;
-            o[3] += cw[s][3][j] * win[j].w;
+            o[0] += cw[s][j] * win[j].x;
+            o[1] += cw[s][TAPS + j] * win[j].y;
+            o[2] += cw[s][2 * TAPS + j] * win[j].z;
+            o[3] += cw[s][3 * TAPS + j] * win[j].w;
           }
           o[0] *= nw[s].x, o[1] *= nw[s].y, o[2] *= nw[s].z, o[3] *= nw[s].w;
           T* dst = static_cast<T*>(p.out[s]) + static_cast<long long>(t) * W + c;
@@ -376,7 +419,13 @@ LLMCTL_API int llmctl_residual_rms(const void* a, int a_is_fp32, long long lda, 
   LLMCTL_BEGIN();
   LLMCTL_REQUIRE(x != nullptr && r != nullptr && W > 0);
   if (tokens == 0) return 0;
-  residual_rms_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>(a, a_is_fp32, lda, f, f_is_fp32, ldf, x, r, W, eps);
+  auto ok4 = [](const void* p, int is32, long long ld) {
+    return p == nullptr || ((reinterpret_cast<uintptr_t>(p) & (is32 ? 15 : 7)) == 0 && ld % 4 == 0);
+  };
+  if (W % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ok4(a, a_is_fp32, lda) && ok4(f, f_is_fp32, ldf))
+    residual_rms_vec_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>(a, a_is_fp32, lda, f, f_is_fp32, ldf, x, r, W, eps);
+  else
+    residual_rms_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>(a, a_is_fp32, lda, f, f_is_fp32, ldf, x, r, W, eps);
   LLMCTL_RETURN_LAST();
 }
 
@@ -390,7 +439,8 @@ LLMCTL_API int llmctl_norm_canon(const float* x, const float* r, int S, const fl
   CanonParams p{x, r, {norm_w0, norm_w1}, {conv_w0, conv_w1}, {out0, out1}, portions, seq_rows, state, S, W, taps};
   cudaStream_t s = (cudaStream_t)stream;
   const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out0) | reinterpret_cast<uintptr_t>(out1) |
-                         reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(norm_w0) | reinterpret_cast<uintptr_t>(norm_w1)) & 15) == 0;
+                         reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(norm_w0) | reinterpret_cast<uintptr_t>(norm_w1) |
+                         reinterpret_cast<uintptr_t>(conv_w0) | reinterpret_cast<uintptr_t>(conv_w1)) & 15) == 0;
   if (W % 4 == 0 && aligned) {
     LLMCTL_DISPATCH_DTYPE(out_is_fp32, T, (launch_norm_canon_vec<T>(p, tokens, s)));
   } else {
